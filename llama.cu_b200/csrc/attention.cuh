@@ -1,0 +1,44 @@
+// Causal GQA attention over the KV cache for the tokens of one round.  Interface only.
+#pragma once
+#include "common.cuh"
+
+namespace lcu {
+
+struct AttnArgs {
+    const void *q;  // [n_tok, nh*dh], row stride stride_q (elements)
+    int stride_q;
+    void *o;  // [n_tok, nh*dh]
+    int stride_o;
+    int n_tok, nh, nkvh, dh;
+    // paged cache (kv_pool != nullptr): token t attends positions [0, tok_pos[t]] of sequence tok_seq[t]
+    const void *kv_pool;
+    KvGeom geom;
+    int layer;
+    const int32_t *tok_seq;
+    const uint32_t *tok_pos;
+    const int32_t *page_table;
+    int pt_stride;
+    // linear cache (kv_pool == nullptr): one request; token t attends [0, pos0 + t]
+    const void *k_lin, *v_lin;
+    int stk, shk, stv, shv;  // token / head strides of the caches (elements)
+    int pos0;
+    // split-KV scratch: partial outputs, (max, sum) pairs and arrival counters
+    int n_splits;
+    float *part_o;        // [n_tok, nh, n_splits, dh]
+    float *part_ml;       // [n_tok, nh, n_splits, 2]
+    unsigned *counters;   // [n_tok, nkvh], zero before the first launch; the kernel re-zeroes them
+};
+
+size_t attn_scratch_bytes(int n_tok, int nh, int nkvh, int dh, int n_splits);
+// Carves part_o / part_ml / counters out of `scratch` (counters must have been zeroed once).
+void attn_bind_scratch(AttnArgs &a, void *scratch);
+// dry: only prepare the kernel variant (shared-memory attribute), launch nothing.
+int attn_launch(const AttnArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
+
+// Appends k, v [seq, nkvh, dh] (strided) to linear caches at pos.. (the write half of
+// operators::attention_kv_cached as called from llama.cu/src/exec/step.rs:162-182).
+int kv_append_linear(void *k_cache, int stkc, int shkc, void *v_cache, int stvc, int shvc, const void *k, int stk,
+                     int shk, const void *v, int stv, int shv, int nkvh, int dh, int seq, int pos, int dt,
+                     cudaStream_t s);
+
+}  // namespace lcu

@@ -1,0 +1,136 @@
+// Shared device/host helpers for the sm_100a decode kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/lcu.h"
+
+namespace lcu {
+
+// ------------------------------------------------------------------ errors
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define LCU_CHECK_CUDA(expr)                                   \
+    do {                                                       \
+        cudaError_t e__ = (expr);                              \
+        if (e__ != cudaSuccess) return ::lcu::cuda_fail(e__, #expr); \
+    } while (0)
+
+#define LCU_REQUIRE(cond, ...)             \
+    do {                                   \
+        if (!(cond)) {                     \
+            ::lcu::set_error(__VA_ARGS__); \
+            return LCU_ERR_INVALID;        \
+        }                                  \
+    } while (0)
+
+inline cudaStream_t as_stream(lcu_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+int sm_count();  // SMs of the current device (cached per device)
+
+// ------------------------------------------------------------------ scalar types
+template <class T> struct Act;  // activation dtype traits
+template <> struct Act<__half> {
+    using T2 = __half2;
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+        return __half22float2(*reinterpret_cast<__half2 *>(&u));
+    }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+template <> struct Act<__nv_bfloat16> {
+    using T2 = __nv_bfloat162;
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+        // bf16 -> f32 is a 16-bit shift
+        return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+
+// round-trip through the activation dtype: the reference materialises every operator
+// output in that type, so fused kernels round at the same places
+template <class T> __device__ __forceinline__ float round_act(float v) { return Act<T>::to_f(Act<T>::from_f(v)); }
+
+// ------------------------------------------------------------------ memory access
+// 128-bit streaming load for data read exactly once per step (weights): no L1 allocation,
+// read-only path.
+__device__ __forceinline__ uint4 ld_stream_128(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ld_stream_64(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_32(const void *p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation
+// attribute may start while its predecessor drains; everything it does before
+// grid_dep_wait() must touch only memory no earlier kernel of the step writes (weights).
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ------------------------------------------------------------------ launch helper
+// Launches with (optionally) the programmatic stream serialisation attribute.
+template <class... KArgs, class... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl,
+                          Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// KV page pool geometry: page p, layer l, kv in {0,1}, head h, slot t -> element offset.
+// A page holds `page_tokens` tokens of every layer: [layer][k|v][kv head][token][dh].
+struct KvGeom {
+    int n_layers, nkvh, dh, page_tokens, page_shift;
+    size_t page_elems;  // n_layers * 2 * nkvh * page_tokens * dh
+    __host__ __device__ __forceinline__ size_t block_off(int page, int layer, int kv, int head) const {
+        return (size_t)page * page_elems + ((size_t)(layer * 2 + kv) * nkvh + head) * ((size_t)page_tokens * dh);
+    }
+};
+
+}  // namespace lcu

@@ -1,0 +1,454 @@
+// Weight-streaming GEMV for 1..4 tokens — the `Linear` operator of the decode step
+// (llama.cu/src/op/linear.rs:17-120: y = x·Wᵀ (+ residual), f32 accumulation, one
+// rounding) with the neighbouring operators fused in:
+//   prologue  RMSNorm of the input rows (op/rms_norm.cuh) — each CTA normalises x itself;
+//   epilogue  residual add (linear.rs:35-46), RoPE + KV-cache append on the fused QKV
+//             projection (op/rope.cuh, the append half of attention_kv_cached,
+//             exec/step.rs:140-184), or SwiGLU on the fused gate|up projection
+//             (op/swiglu.cuh).
+// Every fused value is first rounded to the activation dtype where the reference
+// materialises a tensor, so the fusion does not move a rounding point.
+//
+// The step is HBM-bound: each weight byte is read once per step, so the kernel is built
+// around keeping 128-bit streaming loads in flight on every SM.
+//   - grid: one or two CTAs per SM, each owning a contiguous, balanced range of row PAIRS
+//     (pairs because RoPE rotates adjacent rows and SwiGLU joins row i with row i+di);
+//   - inside a CTA the K dimension is split across KS warps (x RS row sub-groups); a warp
+//     keeps 2*RP rows x KI 16-byte vectors in registers, loaded one group ahead of their
+//     use — the loads of group g+1 are in flight while group g is reduced and stored;
+//   - the first group's loads are issued BEFORE griddepcontrol.wait, so under programmatic
+//     dependent launch the weights of this GEMV already stream while the previous kernel
+//     of the step drains; only then are the activations staged to shared memory;
+//   - Q8_0 weights (int8 quants + one f16 scale per 32) are dequantised in registers.
+#include "gemv.cuh"
+
+#include <map>
+#include <mutex>
+
+namespace lcu {
+
+__device__ __forceinline__ float swiglu_act(float gate, float up) {
+    return gate * __fdividef(1.f, 1.f + expf(-gate)) * up;
+}
+
+// int8 -> f32 without I2F: bytes xor 0x80 become 0..255, placed in the mantissa of 2^23.
+__device__ __forceinline__ void q8x4_to_f32(uint32_t q, float f[4]) {
+    uint32_t u = q ^ 0x80808080u;
+    f[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.f;
+    f[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.f;
+    f[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.f;
+    f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.f;
+}
+
+template <class T>
+__device__ __forceinline__ void vec8_to_f32(const uint4 &v, float f[8]) {
+    float2 a = Act<T>::to_f2(v.x), b = Act<T>::to_f2(v.y), c = Act<T>::to_f2(v.z), d = Act<T>::to_f2(v.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+template <class T>
+__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
+    T *y = reinterpret_cast<T *>(a.y);
+    switch (a.epilogue) {
+    case EPI_STORE: {
+        size_t r = (size_t)pair * 2;
+        y[(size_t)t * a.stride_y + r] = Act<T>::from_f(va);
+        y[(size_t)t * a.stride_y + r + 1] = Act<T>::from_f(vb);
+        break;
+    }
+    case EPI_RESIDUAL: {
+        size_t r = (size_t)pair * 2;
+        const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + r;
+        // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
+        uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
+        float2 rf = Act<T>::to_f2(rr);
+        *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = Act<T>::pack(va + rf.x, vb + rf.y);
+        break;
+    }
+    case EPI_ROPE_KV: {
+        int r = pair * 2;
+        // the qkv projection is materialised in the activation dtype before rope reads it
+        float xa = round_act<T>(va), xb = round_act<T>(vb);
+        int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
+        int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
+        int head = rr / a.dh, e = rr - head * a.dh;
+        uint32_t p = a.pos[t];
+        if (sect < 2) {
+            int half_dh = a.dh >> 1;
+            float sn = a.sin_t[(size_t)p * half_dh + (e >> 1)], cs = a.cos_t[(size_t)p * half_dh + (e >> 1)];
+            float ya = xa * cs - xb * sn, yb = xa * sn + xb * cs;
+            xa = ya;
+            xb = yb;
+        }
+        uint32_t packed = Act<T>::pack(xa, xb);
+        if (sect == 0) {
+            *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
+        } else {
+            int seq = a.tok_seq[t];
+            int page = a.page_table[(size_t)seq * a.pt_stride + (p >> a.geom.page_shift)];
+            int slot = p & (a.geom.page_tokens - 1);
+            size_t off = a.geom.block_off(page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
+            *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.kv_pool) + off) = packed;
+        }
+        break;
+    }
+    case EPI_SWIGLU: {
+        // gate = row pair, up = row pair + di, both materialised before swiglu reads them
+        float g = round_act<T>(va), u = round_act<T>(vb);
+        y[(size_t)t * a.stride_y + pair] = Act<T>::from_f(swiglu_act(g, u));
+        break;
+    }
+    }
+}
+
+template <class T, bool Q8, int NT, int KI, int RP>
+__global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int RS, int n_pairs) {
+    constexpr int R = 2 * RP;
+    constexpr int VE = Q8 ? 16 : 8;  // weights per 16-byte vector
+    extern __shared__ __align__(16) unsigned char smem[];
+    T *xs = reinterpret_cast<T *>(smem);                                        // [NT][in]
+    float *part = reinterpret_cast<float *>(smem + (size_t)NT * a.in * sizeof(T));  // [2][nwarps][R*NT]
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int ks = warp % KS, rs = warp / KS;
+    const int nvec = a.in / VE;
+    const size_t row_bytes = Q8 ? (size_t)a.in : (size_t)a.in * 2;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+
+    const int p_begin = (int)((long long)n_pairs * blockIdx.x / gridDim.x);
+    const int p_end = (int)((long long)n_pairs * (blockIdx.x + 1) / gridDim.x);
+    const int group_pairs = RS * RP;
+    const int n_groups = (p_end - p_begin + group_pairs - 1) / group_pairs;
+
+    uint4 wreg[R][KI];
+    uint16_t sreg[Q8 ? R : 1][Q8 ? KI : 1];
+    const unsigned char *wbase = reinterpret_cast<const unsigned char *>(a.w);
+    const uint16_t *sbase = reinterpret_cast<const uint16_t *>(a.w_scales);
+
+    auto load_group = [&](int g) {
+#pragma unroll
+        for (int rp = 0; rp < RP; ++rp) {
+            int p = p_begin + g * group_pairs + rs * RP + rp;
+            bool pv = p < p_end && rs < RS;
+            size_t ra = swiglu ? (size_t)p : (size_t)p * 2;
+            size_t rb = swiglu ? (size_t)p + a.di : ra + 1;
+#pragma unroll
+            for (int ki = 0; ki < KI; ++ki) {
+                int kv = (ks + KS * ki) * 32 + lane;
+                bool v = pv && kv < nvec;
+                wreg[2 * rp][ki] = v ? ld_stream_128(wbase + ra * row_bytes + (size_t)kv * 16) : make_uint4(0, 0, 0, 0);
+                wreg[2 * rp + 1][ki] = v ? ld_stream_128(wbase + rb * row_bytes + (size_t)kv * 16) : make_uint4(0, 0, 0, 0);
+                if constexpr (Q8) {
+                    sreg[2 * rp][ki] = v ? __ldg(sbase + ra * (size_t)(a.in / 32) + (kv >> 1)) : (uint16_t)0;
+                    sreg[2 * rp + 1][ki] = v ? __ldg(sbase + rb * (size_t)(a.in / 32) + (kv >> 1)) : (uint16_t)0;
+                }
+            }
+        }
+    };
+
+    // weights do not depend on the previous kernel: start streaming before the wait
+    if (n_groups > 0) load_group(0);
+    grid_dep_launch();
+    grid_dep_wait();
+
+    // ---- stage the activations (optionally RMS-normalised) in shared memory
+    {
+        const T *xg = reinterpret_cast<const T *>(a.x);
+        const int nv8 = a.in / 8;
+        for (int t = 0; t < NT; ++t) {
+            uint4 *dst = reinterpret_cast<uint4 *>(xs + (size_t)t * a.in);
+            if (t < a.n_tok) {
+                size_t row = a.x_rows ? a.x_rows[t] : (size_t)t;
+                const uint4 *src = reinterpret_cast<const uint4 *>(xg + row * a.stride_x);
+                for (int i = threadIdx.x; i < nv8; i += blockDim.x) dst[i] = src[i];
+            } else {
+                for (int i = threadIdx.x; i < nv8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        __syncthreads();
+        if (a.prologue == PRO_RMSNORM) {
+            float ss[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                ss[t] = 0.f;
+                const uint4 *src = reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in);
+                for (int i = threadIdx.x; i < nv8; i += blockDim.x) {
+                    float f[8];
+                    vec8_to_f32<T>(src[i], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss[t] += f[j] * f[j];
+                }
+                ss[t] = warp_sum(ss[t]);
+                if (lane == 0) part[t * 16 + warp] = ss[t];
+            }
+            __syncthreads();
+            float rms[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                float v = 0.f;
+                for (int w = 0; w < nwarps; ++w) v += part[t * 16 + w];
+                rms[t] = rsqrtf(v / (float)a.in + a.eps);
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < nv8; i += blockDim.x) {
+                float wf[8];
+                if (a.norm_f32) {
+                    const float4 *nw = reinterpret_cast<const float4 *>(a.norm_w);
+                    float4 w0 = nw[2 * i], w1 = nw[2 * i + 1];
+                    wf[0] = w0.x; wf[1] = w0.y; wf[2] = w0.z; wf[3] = w0.w;
+                    wf[4] = w1.x; wf[5] = w1.y; wf[6] = w1.z; wf[7] = w1.w;
+                } else {
+                    vec8_to_f32<T>(reinterpret_cast<const uint4 *>(a.norm_w)[i], wf);
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    uint4 *row = reinterpret_cast<uint4 *>(xs + (size_t)t * a.in);
+                    float f[8];
+                    vec8_to_f32<T>(row[i], f);
+                    uint4 o;
+                    o.x = Act<T>::pack(rms[t] * f[0] * wf[0], rms[t] * f[1] * wf[1]);
+                    o.y = Act<T>::pack(rms[t] * f[2] * wf[2], rms[t] * f[3] * wf[3]);
+                    o.z = Act<T>::pack(rms[t] * f[4] * wf[4], rms[t] * f[5] * wf[5]);
+                    o.w = Act<T>::pack(rms[t] * f[6] * wf[6], rms[t] * f[7] * wf[7]);
+                    row[i] = o;
+                }
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- main loop over row groups
+    for (int g = 0; g < n_groups; ++g) {
+        float acc[R][NT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) acc[r][t] = 0.f;
+
+#pragma unroll
+        for (int ki = 0; ki < KI; ++ki) {
+            int kv = (ks + KS * ki) * 32 + lane;
+            if (kv < nvec) {
+                if constexpr (!Q8) {
+                    float xf[NT][8];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t)
+                        vec8_to_f32<T>(reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in)[kv], xf[t]);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        float wf[8];
+                        vec8_to_f32<T>(wreg[r][ki], wf);
+#pragma unroll
+                        for (int t = 0; t < NT; ++t)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[r][t] = fmaf(wf[j], xf[t][j], acc[r][t]);
+                    }
+                } else {
+                    float xf[NT][16];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        const uint4 *xv = reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in) + 2 * kv;
+                        vec8_to_f32<T>(xv[0], xf[t]);
+                        vec8_to_f32<T>(xv[1], xf[t] + 8);
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        float wf[16];
+                        q8x4_to_f32(wreg[r][ki].x, wf);
+                        q8x4_to_f32(wreg[r][ki].y, wf + 4);
+                        q8x4_to_f32(wreg[r][ki].z, wf + 8);
+                        q8x4_to_f32(wreg[r][ki].w, wf + 12);
+                        float sc = __half2float(__ushort_as_half(sreg[r][ki]));
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            float d = 0.f;
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) d = fmaf(wf[j], xf[t][j], d);
+                            acc[r][t] = fmaf(sc, d, acc[r][t]);
+                        }
+                    }
+                }
+            }
+        }
+        // next group's weights go in flight before this group is reduced
+        if (g + 1 < n_groups) load_group(g + 1);
+
+        float *pbuf = part + (size_t)(g & 1) * nwarps * (R * NT);
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                float v = warp_sum(acc[r][t]);
+                if (lane == 0) pbuf[warp * (R * NT) + r * NT + t] = v;
+            }
+        __syncthreads();
+        if (ks == 0 && rs < RS && lane < RP * NT) {
+            int rp = lane / NT, t = lane - rp * NT;
+            int p = p_begin + g * group_pairs + rs * RP + rp;
+            if (p < p_end && t < a.n_tok) {
+                float va = 0.f, vb = 0.f;
+                for (int k = 0; k < KS; ++k) {
+                    const float *src = pbuf + (size_t)(rs * KS + k) * (R * NT);
+                    va += src[(2 * rp) * NT + t];
+                    vb += src[(2 * rp + 1) * NT + t];
+                }
+                gemv_epilogue<T>(a, p, t, va, vb);
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+struct GemvPlan {
+    int KS, RS, KI, RP, nwarps;
+};
+
+// Splits the 16-byte vector columns of a row (n32 warp-wide columns) over KS warps x KI
+// vectors with the least padding, preferring few vectors per warp, then fills the CTA
+// with RS row sub-groups up to 16 warps.
+static GemvPlan plan_for(int in, bool q8, int nt) {
+    int nvec = in / (q8 ? 16 : 8);
+    int n32 = (nvec + 31) / 32;
+    GemvPlan best = {1, 16, 1, 1, 16};
+    long best_cost = -1;
+    const int kis[4] = {1, 2, 4, 8};
+    for (int kii = 0; kii < 4; ++kii) {
+        int ki = kis[kii];
+        int ks = (n32 + ki - 1) / ki;
+        if (ks > 16) continue;
+        int rs = 16 / ks;
+        int waste = ks * ki - n32;          // padded vector columns per row
+        int idle = 16 - ks * rs;            // warps the CTA cannot use
+        long cost = (long)waste * 1000 / (ks * ki) * 4 + idle * 30 + ki * 5;
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = {ks, rs, ki, 1, ks * rs};
+        }
+    }
+    int rp = 4 / best.KI;
+    if (rp < 1) rp = 1;
+    int cap = 8 / nt;  // keep 2*RP*NT accumulators <= 16
+    if (cap < 1) cap = 1;
+    if (rp > cap) rp = cap;
+    if (q8 && rp > 2) rp = 2;
+    best.RP = rp;
+    return best;
+}
+
+template <class T, bool Q8, int NT, int KI, int RP>
+static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
+    auto kernel = gemv_kernel<T, Q8, NT, KI, RP>;
+    // activations + double-buffered per-warp partial sums (also the RMSNorm scratch)
+    size_t smem = (size_t)NT * a.in * sizeof(T) + (size_t)2 * 16 * (2 * RP * NT) * sizeof(float);
+    int block = pl.nwarps * 32;
+
+    struct Info { int ctas_per_sm; };
+    static std::mutex mu;
+    static std::map<std::pair<int, std::pair<int, size_t>>, Info> cache;  // (device, (block, smem))
+    int dev = 0;
+    cudaGetDevice(&dev);
+    Info info;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto key = std::make_pair(dev, std::make_pair(block, smem));
+        auto it = cache.find(key);
+        if (it == cache.end()) {
+            if (smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(gemv smem)");
+            }
+            int occ = 0;
+            cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, block, smem);
+            if (e != cudaSuccess) return cuda_fail(e, "occupancy(gemv)");
+            if (occ < 1) {
+                set_error("gemv: configuration does not fit on an SM (in = %d, smem = %zu)", a.in, smem);
+                return LCU_ERR_INVALID;
+            }
+            info.ctas_per_sm = occ > 2 ? 2 : occ;
+            cache[key] = info;
+        } else {
+            info = it->second;
+        }
+    }
+    int group_pairs = pl.RS * RP;
+    int max_ctas = sm_count() * info.ctas_per_sm;
+    int want = (n_pairs + group_pairs - 1) / group_pairs;
+    int grid = want < max_ctas ? want : max_ctas;
+    if (grid < 1) grid = 1;
+    if (dry) return LCU_OK;  // attributes and occupancy are now cached for this configuration
+    LCU_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(block), smem, s, pdl, a, pl.KS, pl.RS, n_pairs));
+    return LCU_OK;
+}
+
+template <class T, bool Q8, int NT>
+static int launch_nt(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
+#define LCU_GEMV_CASE(KI_, RP_) \
+    if (pl.KI == KI_ && pl.RP == RP_) return launch_inst<T, Q8, NT, KI_, RP_>(a, pl, n_pairs, s, pdl, dry);
+    if constexpr (Q8) {
+        LCU_GEMV_CASE(1, 2) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
+    } else if constexpr (NT == 1) {
+        LCU_GEMV_CASE(1, 4) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
+    } else if constexpr (NT == 2) {
+        LCU_GEMV_CASE(1, 4) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
+    } else {
+        LCU_GEMV_CASE(1, 2) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
+    }
+#undef LCU_GEMV_CASE
+    set_error("gemv: no kernel for KI = %d, RP = %d, NT = %d", pl.KI, pl.RP, NT);
+    return LCU_ERR_INVALID;
+}
+
+template <class T, bool Q8>
+static int launch_t(const GemvArgs &a, cudaStream_t s, bool pdl, bool dry) {
+    int nt = a.n_tok <= 1 ? 1 : (a.n_tok == 2 ? 2 : 4);
+    GemvPlan pl = plan_for(a.in, Q8, nt);
+    int n_pairs = a.out / 2;
+    switch (nt) {
+    case 1: return launch_nt<T, Q8, 1>(a, pl, n_pairs, s, pdl, dry);
+    case 2: return launch_nt<T, Q8, 2>(a, pl, n_pairs, s, pdl, dry);
+    default: return launch_nt<T, Q8, 4>(a, pl, n_pairs, s, pdl, dry);
+    }
+}
+
+int gemv_max_tokens(int in) {
+    for (int nt = 4; nt > 1; nt >>= 1)
+        if ((size_t)nt * in * 2 + 8192 <= (size_t)227 * 1024) return nt;
+    return 1;
+}
+
+int gemv_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
+    LCU_REQUIRE(a.n_tok >= 1 && a.n_tok <= 4, "gemv: n_tok = %d (1..4)", a.n_tok);
+    LCU_REQUIRE(a.out > 0 && a.out % 2 == 0, "gemv: out = %d must be even", a.out);
+    LCU_REQUIRE(a.in > 0 && a.in % (a.w_q8 ? 32 : 8) == 0, "gemv: in = %d must be a multiple of %d", a.in,
+                a.w_q8 ? 32 : 8);
+    LCU_REQUIRE(a.stride_x % 8 == 0, "gemv: x row stride %d must be a multiple of 8 elements", a.stride_x);
+    LCU_REQUIRE(a.n_tok <= gemv_max_tokens(a.in), "gemv: in = %d too large for %d tokens at once", a.in, a.n_tok);
+    if (a.epilogue == EPI_SWIGLU) LCU_REQUIRE(a.out == 2 * a.di, "gemv: swiglu needs out == 2*di");
+    if (a.epilogue == EPI_ROPE_KV)
+        LCU_REQUIRE(a.out == a.qd + 2 * a.kvd && a.dh % 2 == 0, "gemv: rope/kv epilogue shape mismatch");
+    if (dt == LCU_F16) return a.w_q8 ? launch_t<__half, true>(a, s, pdl, dry) : launch_t<__half, false>(a, s, pdl, dry);
+    if (dt == LCU_BF16) {
+        LCU_REQUIRE(!a.w_q8, "gemv: Q8_0 weights are supported with f16 activations only");
+        return launch_t<__nv_bfloat16, false>(a, s, pdl, dry);
+    }
+    set_error("gemv: activation dtype %d unsupported", dt);
+    return LCU_ERR_INVALID;
+}
+
+}  // namespace lcu
+
+namespace lcu {
+// Sets the shared-memory attribute and caches the occupancy of every kernel variant a
+// context with these shapes can launch, so that nothing of the kind happens inside a
+// stream capture.
+int gemv_warm(int in, int out, bool q8, int dt) {
+    for (int nt = 1; nt <= gemv_max_tokens(in); nt *= 2) {
+        GemvArgs a{};
+        a.in = in; a.out = out; a.n_tok = nt; a.w_q8 = q8; a.stride_x = in; a.epilogue = EPI_STORE;
+        int rc = gemv_launch(a, dt, nullptr, false, true);
+        if (rc) return rc;
+    }
+    return LCU_OK;
+}
+}  // namespace lcu

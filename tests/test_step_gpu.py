@@ -1,0 +1,122 @@
+"""End-to-end parity of the CUDA token loop against the CPU oracle (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import greedy_parity, prompts_for
+
+pytestmark = pytest.mark.gpu
+
+# logits tolerance from the north star: max-abs 2e-2 for f16 and for bf16
+TOL = 2e-2
+
+
+def run_pair(L, O, cfg, prompts, steps, seed=0, teacher=True, **kw):
+    w = L.synth_weights_numpy(cfg, seed)
+    orc = O.Model(cfg, w)
+    o_ids, o_lgs = orc.generate(prompts, steps)
+    ctx = L.load_model(cfg, w, kv_bytes=None, **kw)
+    g_ids = L.generate(ctx, prompts, steps)
+    return ctx, orc, w, g_ids, o_ids, o_lgs
+
+
+def teacher_forced_logits(L, ctx, cfg, prompts, o_ids, steps):
+    """Feeds the ORACLE's tokens to the GPU and returns its logits per step [n][steps][vocab]."""
+    n = len(prompts)
+    seqs = [ctx.seq_create() for _ in prompts]
+    out = torch.zeros(max(n, 1), 2, dtype=torch.int32, device="cuda:0")
+    lgs = [[] for _ in prompts]
+    for i, p in enumerate(prompts):
+        ctx.step([(seqs[i], 0, len(p))], p, out)
+        lgs[i].append(ctx.logits(1)[0].float().cpu().numpy())
+    pos = [len(p) for p in prompts]
+    for s in range(steps - 1):
+        reqs = [(seqs[i], pos[i], 1) for i in range(n)]
+        ctx.step(reqs, np.array([o_ids[i][s] for i in range(n)], np.uint32), out)
+        lg = ctx.logits(n).float().cpu().numpy()
+        for i in range(n):
+            lgs[i].append(lg[i])
+            pos[i] += 1
+    for s in seqs:
+        ctx.seq_free(s)
+    return lgs
+
+
+def check_parity(L, O, cfg, lengths, steps, **kw):
+    prompts = prompts_for(cfg, lengths)
+    ctx, orc, w, g_ids, o_ids, o_lgs = run_pair(L, O, cfg, prompts, steps, **kw)
+    g_lgs = teacher_forced_logits(L, ctx, cfg, prompts, o_ids, steps)
+    worst = 0.0
+    for i in range(len(prompts)):
+        for s in range(steps):
+            worst = max(worst, float(np.abs(g_lgs[i][s] - o_lgs[i][s]).max()))
+    assert worst <= TOL, f"logits differ by {worst}"
+    for i in range(len(prompts)):
+        k, margin = greedy_parity(g_ids[i], o_ids[i], o_lgs[i], TOL)
+        assert k == steps or margin <= 2 * worst + 1e-6, (
+            f"seq {i}: greedy ids diverge at step {k} where the oracle's top-2 margin is {margin}")
+    ctx.close()
+    return worst
+
+
+def test_tiny_greedy_32_steps(L, O):
+    """configs[0]: 16-token prompt, 32 greedy steps, ids identical and logits within tolerance."""
+    cfg = L.CONFIGS["tiny"]
+    prompts = prompts_for(cfg, [16])
+    ctx, orc, w, g_ids, o_ids, o_lgs = run_pair(L, O, cfg, prompts, 32)
+    k, margin = greedy_parity(g_ids[0], o_ids[0], o_lgs[0], TOL)
+    assert k == 32 or margin <= 2e-3, f"diverged at step {k}, margin {margin}: {g_ids[0]} vs {o_ids[0]}"
+    g_lgs = teacher_forced_logits(L, ctx, cfg, prompts, o_ids, 32)
+    worst = max(float(np.abs(g_lgs[0][s] - o_lgs[0][s]).max()) for s in range(32))
+    assert worst <= TOL
+    ctx.close()
+
+
+def test_tiny_batch_ragged(L, O):
+    """Several sequences with ragged prompt lengths, pages crossing boundaries."""
+    cfg = L.CONFIGS["tiny"]
+    check_parity(L, O, cfg, [1, 7, 16, 33, 64, 65], 20, page_tokens=16)
+
+
+@pytest.mark.parametrize("name,layers,vocab,lengths,steps", [
+    ("llama1b", 2, 4096, [24, 130], 12),      # bf16, dh 64, GQA 4
+    ("llama8b", 2, 4096, [20, 70, 129], 10),  # f16, dh 128, GQA 4
+    ("llama8b_q8", 2, 4096, [20, 40], 10),    # Q8_0 weights
+])
+def test_reduced_shapes(L, O, name, layers, vocab, lengths, steps):
+    from llama_cu_b200.model import reduced
+    cfg = reduced(L.CONFIGS[name], layers, vocab)
+    check_parity(L, O, cfg, lengths, steps)
+
+
+def test_graph_equals_eager(L):
+    """The captured decode graph and the eager launch sequence give identical ids."""
+    cfg = L.CONFIGS["tiny"]
+    w = L.synth_weights_numpy(cfg, 0)
+    prompts = prompts_for(cfg, [16, 40])
+    ctx = L.load_model(cfg, w)
+    a = L.generate(ctx, prompts, 24)
+    ctx.set_cuda_graph(False)
+    b = L.generate(ctx, prompts, 24)
+    assert a == b
+    ctx.close()
+
+
+def test_overflow_and_pages(L):
+    cfg = L.CONFIGS["tiny"]
+    w = L.synth_weights_numpy(cfg, 0)
+    ctx = L.load_model(cfg, w, kv_bytes=None, nctx=128, page_tokens=16)
+    ctx2_pages = ctx.pages_total
+    s = ctx.seq_create()
+    out = torch.zeros(1, 2, dtype=torch.int32, device="cuda:0")
+    with pytest.raises(L.LcuError) as e:
+        ctx.step([(s, 0, 129)], np.zeros(129, np.uint32) + 5, out)
+    assert e.value.code == L.ERR_OVERFLOW
+    ctx.step([(s, 0, 100)], np.zeros(100, np.uint32) + 5, out)
+    assert ctx.pages_free == ctx2_pages - 7
+    ctx.seq_resize(s, 10)  # rollback shrinks like KVCache::update
+    assert ctx.pages_free == ctx2_pages - 1
+    ctx.seq_free(s)
+    assert ctx.pages_free == ctx2_pages
+    torch.cuda.synchronize()
+    ctx.close()
