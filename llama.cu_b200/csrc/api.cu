@@ -144,6 +144,7 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
         a.stride_y = stride_y;
         a.res = residual ? reinterpret_cast<const unsigned char *>(residual) + (size_t)t0 * stride_res * eb : nullptr;
         a.stride_res = stride_res;
+        a.early_prefetch = 1;
         int rc = gemv_launch(a, dt, as_stream(s), false);
         if (rc) return rc;
         t0 += nt;

@@ -241,18 +241,21 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-size_t attn_scratch_bytes(int n_tok, int nh, int nkvh, int dh, int n_splits) {
-    return align256((size_t)n_tok * nh * n_splits * dh * 4) + align256((size_t)n_tok * nh * n_splits * 2 * 4) +
-           align256((size_t)n_tok * nkvh * 4);
+// Scratch layout: arrival counters FIRST, at a fixed place and sized for the largest round,
+// so that partial outputs of a round with another (tokens, splits) shape can never land on
+// them — the counters must read zero whenever a launch starts.
+size_t attn_scratch_bytes(int n_tok, int nh, int nkvh, int dh, int n_splits, int max_tok) {
+    return align256((size_t)max_tok * nkvh * 4) + align256((size_t)n_tok * nh * n_splits * 2 * 4) +
+           align256((size_t)n_tok * nh * n_splits * dh * 4);
 }
 
-void attn_bind_scratch(AttnArgs &a, void *scratch) {
+void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok) {
     unsigned char *p = reinterpret_cast<unsigned char *>(scratch);
-    a.part_o = reinterpret_cast<float *>(p);
-    p += align256((size_t)a.n_tok * a.nh * a.n_splits * a.dh * 4);
+    a.counters = reinterpret_cast<unsigned *>(p);
+    p += align256((size_t)max_tok * a.nkvh * 4);
     a.part_ml = reinterpret_cast<float *>(p);
     p += align256((size_t)a.n_tok * a.nh * a.n_splits * 2 * 4);
-    a.counters = reinterpret_cast<unsigned *>(p);
+    a.part_o = reinterpret_cast<float *>(p);
 }
 
 template <class T, int DH, int G>

@@ -29,9 +29,11 @@ struct AttnArgs {
     unsigned *counters;   // [n_tok, nkvh], zero before the first launch; the kernel re-zeroes them
 };
 
-size_t attn_scratch_bytes(int n_tok, int nh, int nkvh, int dh, int n_splits);
-// Carves part_o / part_ml / counters out of `scratch` (counters must have been zeroed once).
-void attn_bind_scratch(AttnArgs &a, void *scratch);
+// Bytes of split-KV scratch for a round of n_tok tokens when the largest round has max_tok.
+size_t attn_scratch_bytes(int n_tok, int nh, int nkvh, int dh, int n_splits, int max_tok);
+// Carves counters / part_ml / part_o out of `scratch`; the counters sit first, at a place that
+// does not depend on the round's shape, and must have been zeroed once.
+void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok);
 // dry: only prepare the kernel variant (shared-memory attribute), launch nothing.
 int attn_launch(const AttnArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
 

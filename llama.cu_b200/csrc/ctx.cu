@@ -3,6 +3,7 @@
 // step,output_head,kv_cache}.rs and memory.rs for one GPU.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -276,7 +277,7 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     for (int n = 1; n <= c->max_tokens; ++n) {
         int sp = attn_splits(c, n);
         if (sp > 1) {
-            size_t b = attn_scratch_bytes(n, c->nh_l, c->nkvh_l, d.dh, sp);
+            size_t b = attn_scratch_bytes(n, c->nh_l, c->nkvh_l, d.dh, sp, c->max_tokens);
             if (b > sz_attn) sz_attn = b;
         }
     }
@@ -524,7 +525,11 @@ struct Round {
 int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t s, int *count) {
     const lcu_model_desc &d = c->desc;
     const int dt = c->dt;
-    const bool pdl = true;
+    // Programmatic dependent launch measured slower than plain graph edges for this chain of
+    // short kernels on B200 (3.8 ms vs 3.3 ms per 8B step), so it is off unless LCU_PDL=1.
+    static const bool pdl = getenv("LCU_PDL") && getenv("LCU_PDL")[0] == '1';
+    static const int pdl_trigger = getenv("LCU_PDL_TRIGGER") ? atoi(getenv("LCU_PDL_TRIGGER")) : 2;
+    static const int early_prefetch = getenv("LCU_PREFETCH") ? atoi(getenv("LCU_PREFETCH")) : 1;
     int launches = 0;
     unsigned char *D = c->desc_dev;
     uint32_t *tokens = reinterpret_cast<uint32_t *>(D + r.L.tokens);
@@ -572,6 +577,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.pos = pos + t0; a.sin_t = c->sin_t; a.cos_t = c->cos_t;
             a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req + t0; a.page_table = page_table;
             a.pt_stride = c->pt_stride;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
             rc = gemv_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;
@@ -584,7 +590,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.n_tok = r.n_tok; a.nh = c->nh_l; a.nkvh = c->nkvh_l; a.dh = d.dh;
             a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req; a.tok_pos = pos;
             a.page_table = page_table; a.pt_stride = c->pt_stride; a.n_splits = n_splits;
-            if (n_splits > 1) attn_bind_scratch(a, c->attn_scratch);
+            if (n_splits > 1) attn_bind_scratch(a, c->attn_scratch, c->max_tokens);
             rc = attn_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;
@@ -600,6 +606,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.prologue = PRO_NONE;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.y = row(c->x, d.d, t0); a.stride_y = d.d; a.res = a.y; a.stride_res = d.d;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
             rc = gemv_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;
@@ -620,6 +627,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.x = row(c->x, d.d, t0); a.stride_x = d.d; a.n_tok = nt; a.in = d.d; a.out = 2 * c->di_l;
             a.prologue = PRO_RMSNORM; a.norm_w = W.ffn_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
             a.epilogue = EPI_SWIGLU; a.di = c->di_l; a.y = row(c->act, c->di_l, t0); a.stride_y = c->di_l;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
             rc = gemv_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;
@@ -636,6 +644,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.prologue = PRO_NONE;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.y = row(c->x, d.d, t0); a.stride_y = d.d; a.res = a.y; a.stride_res = d.d;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
             rc = gemv_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;
@@ -659,6 +668,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.x = c->x; a.stride_x = d.d; a.x_rows = out_idx + r0; a.n_tok = nt; a.in = d.d; a.out = d.vocab;
             a.prologue = PRO_RMSNORM; a.norm_w = c->out_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
             a.epilogue = EPI_STORE; a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
             rc = gemv_launch(a, dt, s, pdl);
             if (rc) return rc;
             ++launches;

@@ -22,6 +22,7 @@
 //   - Q8_0 weights (int8 quants + one f16 scale per 32) are dequantised in registers.
 #include "gemv.cuh"
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 
@@ -147,9 +148,10 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
     };
 
     // weights do not depend on the previous kernel: start streaming before the wait
-    if (n_groups > 0) load_group(0);
-    grid_dep_launch();
+    if (a.early_prefetch && n_groups > 0) load_group(0);
+    if (a.pdl_trigger == 0) grid_dep_launch();
     grid_dep_wait();
+    if (!a.early_prefetch && n_groups > 0) load_group(0);
 
     // ---- stage the activations (optionally RMS-normalised) in shared memory
     {
@@ -296,9 +298,15 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
             }
         }
     }
+    if (a.pdl_trigger == 1) grid_dep_launch();
 }
 
 // ------------------------------------------------------------------ host side
+
+static int tune_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
 
 struct GemvPlan {
     int KS, RS, KI, RP, nwarps;
@@ -365,7 +373,8 @@ static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaS
                 set_error("gemv: configuration does not fit on an SM (in = %d, smem = %zu)", a.in, smem);
                 return LCU_ERR_INVALID;
             }
-            info.ctas_per_sm = occ > 2 ? 2 : occ;
+            int cap = tune_int("LCU_GEMV_CTAS_PER_SM", 2);
+            info.ctas_per_sm = occ > cap ? cap : occ;
             cache[key] = info;
         } else {
             info = it->second;

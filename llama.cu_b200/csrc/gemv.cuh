@@ -42,6 +42,9 @@ struct GemvArgs {
     int pt_stride;
     // EPI_SWIGLU: rows [0,di) gate, [di,2di) up; y gets [n_tok, di]
     int di;
+    // tuning: 0 = trigger dependents at kernel start, 1 = after the main loop, 2 = never (implicit at exit)
+    int pdl_trigger;
+    int early_prefetch;  // 1 = first weight loads before griddepcontrol.wait
 };
 
 // Enqueues one GEMV; dt = LCU_F16 / LCU_BF16.  pdl: launch with programmatic serialisation.

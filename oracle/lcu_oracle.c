@@ -13,6 +13,7 @@
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 #ifdef _OPENMP
 #include <omp.h>
@@ -296,6 +297,7 @@ struct orc_model {
     int used[ORC_MAX_SEQ];
     float *hidden; /* [n_layers+1][n_tok][d] of the last forward */
     int hidden_tok;
+    double t_layers, t_head; /* wall seconds of the last forward: all layers / the head */
 };
 
 orc_model *orc_model_new(const orc_desc *desc) {
@@ -352,6 +354,54 @@ int orc_model_set_weight(orc_model *m, int layer, int kind, const void *data, in
     return 0;
 }
 
+/* Fills every weight with cheap seeded pseudo-random values of standard deviation 0.02
+ * (uniform, not normal) and norm weights of 1: for TIMING the CPU baseline on shapes too
+ * large to draw with numpy; parity tests never use it. */
+static void fill_uniform(float *w, size_t n, uint64_t seed) {
+    const float a = 0.02f * 1.7320508f; /* uniform on [-a, a] has std 0.02 */
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        uint64_t z = (i + seed * 0x9E3779B97F4A7C15ull) + 0x9E3779B97F4A7C15ull; /* splitmix64 */
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        w[i] = ((float)(z >> 40) * (1.0f / 16777216.0f) * 2.0f - 1.0f) * a;
+    }
+}
+
+int orc_model_fill_synthetic(orc_model *m, uint64_t seed) {
+    const orc_desc *c = &m->c;
+    for (int kind = 0; kind <= ORC_W_LM_HEAD; ++kind)
+        for (int l = 0; l < c->n_layers; ++l) {
+            size_t want;
+            float **slot;
+            switch (kind) {
+            case ORC_W_EMBD: want = (size_t)c->vocab * c->d; slot = &m->embd; break;
+            case ORC_W_OUT_NORM: want = (size_t)c->d; slot = &m->out_norm; break;
+            case ORC_W_LM_HEAD: want = (size_t)c->vocab * c->d; slot = &m->lm_head; break;
+            case ORC_W_ATTN_NORM: want = (size_t)c->d; slot = &m->layers[l].attn_norm; break;
+            case ORC_W_QKV: want = (size_t)(c->nh + 2 * c->nkvh) * c->dh * c->d; slot = &m->layers[l].qkv; break;
+            case ORC_W_O: want = (size_t)c->d * c->nh * c->dh; slot = &m->layers[l].o; break;
+            case ORC_W_FFN_NORM: want = (size_t)c->d; slot = &m->layers[l].ffn_norm; break;
+            case ORC_W_GATE_UP: want = (size_t)2 * c->di * c->d; slot = &m->layers[l].gate_up; break;
+            default: want = (size_t)c->d * c->di; slot = &m->layers[l].down; break;
+            }
+            int global = kind == ORC_W_EMBD || kind == ORC_W_OUT_NORM || kind == ORC_W_LM_HEAD;
+            if (global && l > 0) continue;
+            if (kind == ORC_W_EMBD) continue; /* tied to the LM head below: saves a vocab x d fill */
+            free(*slot);
+            *slot = (float *)malloc(want * 4);
+            if (!*slot) return -1;
+            if (kind == ORC_W_ATTN_NORM || kind == ORC_W_FFN_NORM || kind == ORC_W_OUT_NORM)
+                for (size_t i = 0; i < want; ++i) (*slot)[i] = 1.0f;
+            else
+                fill_uniform(*slot, want, seed + (uint64_t)kind * 1000 + (uint64_t)l);
+        }
+    if (m->embd && m->embd != m->lm_head) free(m->embd);
+    m->embd = m->lm_head;
+    return 0;
+}
+
 int orc_seq_new(orc_model *m) {
     for (int s = 0; s < ORC_MAX_SEQ; ++s)
         if (!m->used[s]) {
@@ -397,6 +447,8 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
     m->hidden = (float *)malloc((size_t)(c->n_layers + 1) * n * d * 4);
     m->hidden_tok = n;
 
+    struct timespec ts0, ts1, ts2;
+    clock_gettime(CLOCK_MONOTONIC, &ts0);
     orc_embedding(x, m->embd, tokens, n, d);
     memcpy(m->hidden, x, (size_t)n * d * 4);
     for (int l = 0; l < c->n_layers; ++l) {
@@ -422,6 +474,7 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
         orc_linear(x, act, L->down, x2, n, di, d, dt);
         memcpy(m->hidden + (size_t)(l + 1) * n * d, x, (size_t)n * d * 4);
     }
+    clock_gettime(CLOCK_MONOTONIC, &ts1);
     /* head: gather the last token of each request, norm, lm_head, argmax */
     float *xo = (float *)malloc((size_t)n_req * d * 4), *lg = (float *)malloc((size_t)n_req * c->vocab * 4);
     for (int r = 0, t0 = 0; r < n_req; t0 += (int)seq_len[r], ++r)
@@ -432,8 +485,16 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
         if (ids) orc_argmax(lg + (size_t)r * c->vocab, (size_t)c->vocab, &ids[r], NULL);
     }
     if (logits) memcpy(logits, lg, (size_t)n_req * c->vocab * 4);
+    clock_gettime(CLOCK_MONOTONIC, &ts2);
+    m->t_layers = (double)(ts1.tv_sec - ts0.tv_sec) + 1e-9 * (double)(ts1.tv_nsec - ts0.tv_nsec);
+    m->t_head = (double)(ts2.tv_sec - ts1.tv_sec) + 1e-9 * (double)(ts2.tv_nsec - ts1.tv_nsec);
     free(pos); free(x); free(h); free(qkv); free(att); free(gu); free(act); free(x2); free(xo); free(lg);
     return 0;
+}
+
+void orc_last_times(orc_model *m, double *t_layers, double *t_head) {
+    *t_layers = m->t_layers;
+    *t_head = m->t_head;
 }
 
 int orc_last_hidden(orc_model *m, float *out, size_t cap) {

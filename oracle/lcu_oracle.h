@@ -73,6 +73,8 @@ orc_model *orc_model_new(const orc_desc *desc);
 void orc_model_free(orc_model *m);
 /* data: `count` logical elements of `dtype` (Q8_0: count weights = count/32 blocks of 34 bytes) */
 int orc_model_set_weight(orc_model *m, int layer, int kind, const void *data, int dtype, size_t count);
+/* timing aid: seeded uniform weights of std 0.02, norm weights 1 (no numpy round trip) */
+int orc_model_fill_synthetic(orc_model *m, uint64_t seed);
 int orc_seq_new(orc_model *m);          /* returns a sequence slot id */
 void orc_seq_free(orc_model *m, int seq);
 /* One round: request r owns tokens[off_r .. off_r+seq_len[r]) at positions pos0[r]...
@@ -84,6 +86,8 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
 /* debugging / per-stage parity: copies of the hidden state after every layer of the last
  * forward, [n_layers+1][n_tok][d]; returns n_tok */
 int orc_last_hidden(orc_model *m, float *out, size_t cap);
+/* wall-clock seconds the last orc_forward spent in the layers and in the head */
+void orc_last_times(orc_model *m, double *t_layers, double *t_head);
 
 #ifdef __cplusplus
 }

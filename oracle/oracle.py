@@ -52,9 +52,11 @@ def lib():
         L.orc_model_free.argtypes = [C.c_void_p]
         L.orc_model_set_weight.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_size_t]
         L.orc_seq_new.argtypes = [C.c_void_p]
+        L.orc_model_fill_synthetic.argtypes = [C.c_void_p, C.c_uint64]
         L.orc_seq_free.argtypes = [C.c_void_p, C.c_int]
         L.orc_forward.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 6
         L.orc_last_hidden.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_last_times.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double)]
         L.orc_to_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]
         L.orc_from_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]
         L.orc_build_sin_cos.argtypes = [C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
@@ -162,12 +164,16 @@ def sample(logits, random, temperature, topp, topk):
 class Model:
     """Whole-model oracle: weights converted to f32 once, one KV cache per sequence."""
 
-    def __init__(self, cfg, weights, act_dtype=None):
-        """cfg: a ModelConfig-like object; weights: {(layer, kind): uint16 bits | Q8_0 dict}."""
+    def __init__(self, cfg, weights, act_dtype=None, fill_seed=0):
+        """cfg: a ModelConfig-like object; weights: {(layer, kind): uint16 bits | Q8_0 dict},
+        or None to fill the model with cheap seeded values (timing only)."""
         self.cfg = cfg
         self.dt = cfg.act_dtype if act_dtype is None else act_dtype
         d = Desc(cfg.n_layers, cfg.d, cfg.nh, cfg.nkvh, cfg.dh, cfg.di, cfg.vocab, cfg.nctx, cfg.eps, cfg.theta, self.dt)
         self.m = lib().orc_model_new(C.byref(d))
+        if weights is None:
+            assert lib().orc_model_fill_synthetic(self.m, fill_seed) == 0
+            return
         for (layer, kind), w in weights.items():
             if isinstance(w, dict):
                 data, dt, count = w["blocks"], Q8_0, w["q"].size
@@ -202,6 +208,12 @@ class Model:
         if rc != 0:
             raise RuntimeError(f"orc_forward failed: {rc}")
         return logits, ids
+
+    def last_times(self):
+        """(seconds in the layers, seconds in the head) of the last forward."""
+        a, b = C.c_double(), C.c_double()
+        lib().orc_last_times(self.m, C.byref(a), C.byref(b))
+        return a.value, b.value
 
     def last_hidden(self, n_tok):
         out = np.empty((self.cfg.n_layers + 1, n_tok, self.cfg.d), np.float32)

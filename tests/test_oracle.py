@@ -1,0 +1,179 @@
+"""CPU tests of the oracle: against the committed golden vectors (made by the independent
+PyTorch restatement), against that restatement on fresh seeds, and operator by operator
+against numpy / torch / gguf definitions."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import prompts_for
+from torch_ref import TorchModel
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "decode_golden.json")
+
+
+def _case_cfg(L, case):
+    from llama_cu_b200.model import reduced
+    cfg = L.CONFIGS[case["config"]]
+    if case["reduced"]:
+        cfg = reduced(cfg, case["reduced"][0], case["reduced"][1])
+    return cfg
+
+
+@pytest.mark.parametrize("name", ["tiny", "tiny_batch", "llama1b_L1", "llama8b_q8_L1"])
+def test_oracle_matches_golden(L, O, name):
+    case = json.load(open(GOLDEN))[name]
+    cfg = _case_cfg(L, case)
+    w = L.synth_weights_numpy(cfg, case["weight_seed"])
+    rng = np.random.default_rng(case["prompt_seed"])
+    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in case["lengths"]]
+    ids, lgs = O.Model(cfg, w).generate(prompts, case["steps"])
+    ulp = 2.0 ** -10 if cfg.act_dtype == 0 else 2.0 ** -7
+    for i in range(len(prompts)):
+        for s in range(case["steps"]):
+            if ids[i][s] != case["ids"][i][s]:
+                # only a tie-sized margin may flip an id (independent summation orders)
+                assert case["top2_margin"][i][s] <= 4 * ulp * 8, (name, i, s)
+                break
+            probes = [0, 1, cfg.vocab // 2, cfg.vocab - 1, ids[i][s]]
+            got = np.array([lgs[i][s][j] for j in probes])
+            want = np.array(case["logit_probes"][i][s])
+            assert np.all(np.abs(got - want) <= 4 * ulp * np.maximum(np.abs(want), 1.0)), (name, i, s, got, want)
+        else:
+            continue
+
+
+def test_tiny_golden_ids(L, O):
+    """configs[0]: 16-token prompt, 32 greedy steps.  The two independent CPU implementations
+    agree on every id until a step whose top-2 margin is a tie in f16 (<= 1 ulp): there the
+    winner depends on the summation order, which neither the reference nor cuBLAS pins."""
+    case = json.load(open(GOLDEN))["tiny"]
+    cfg = L.CONFIGS["tiny"]
+    w = L.synth_weights_numpy(cfg, 0)
+    prompts = prompts_for(cfg, [16], seed=1)
+    ids, _ = O.Model(cfg, w).generate(prompts, 32)
+    first_tie = next((s for s, m in enumerate(case["top2_margin"][0]) if m <= 2.0 ** -10), 32)
+    assert ids[0][:first_tie] == case["ids"][0][:first_tie]
+    for s in range(32):
+        if ids[0][s] != case["ids"][0][s]:
+            assert case["top2_margin"][0][s] <= 2.0 ** -10
+            break
+
+
+@pytest.mark.parametrize("dt", [0, 1, 2])
+def test_oracle_vs_torch_fresh_seed(L, O, dt):
+    from llama_cu_b200.model import ModelConfig
+    cfg = ModelConfig("t", 2, 128, 4, 2, 64, 208, 512, 1e4, act_dtype=0 if dt == 2 else dt, nctx=128)
+    w = L.synth_weights_numpy(cfg, 11)
+    orc, ref = O.Model(cfg, w, act_dtype=dt), TorchModel(cfg, w, act_dtype=dt)
+    s0, s1 = orc.seq_new(), orc.seq_new()
+    toks = np.arange(3, 3 + 9 + 4).astype(np.uint32)
+    lg_o, ids_o = orc.forward([(s0, 0, 9), (s1, 0, 4)], toks)
+    lg_t, ids_t = ref.forward([(s0, 0, 9), (s1, 0, 4)], toks)
+    tol = {0: 4e-3, 1: 3e-2, 2: 1e-4}[dt]
+    assert np.abs(lg_o - lg_t).max() <= tol
+    lg_o, _ = orc.forward([(s0, 9, 1), (s1, 4, 1)], ids_o)
+    lg_t, _ = ref.forward([(s0, 9, 1), (s1, 4, 1)], ids_o)
+    assert np.abs(lg_o - lg_t).max() <= tol
+    h = orc.last_hidden(2)
+    assert h.shape == (cfg.n_layers + 1, 2, cfg.d) and np.isfinite(h).all()
+
+
+def test_rounding_matches_torch(O):
+    rng = np.random.default_rng(0)
+    a = np.concatenate([rng.standard_normal(4096).astype(np.float32) * 10, [0.0, -0.0, 65504.0, 1e-8, 6.1e-5]]).astype(np.float32)
+    t = torch.from_numpy(a)
+    assert np.array_equal(O.round_to(a, 0), t.half().float().numpy())
+    assert np.array_equal(O.round_to(a, 1), t.bfloat16().float().numpy())
+    assert np.array_equal(O.from_f32(a, 1).view(np.int16), t.bfloat16().view(torch.int16).numpy())
+
+
+def test_q8_0_dequant_matches_gguf(L, O):
+    from llama_cu_b200.model import q8_0_blocks
+    rng = np.random.default_rng(2)
+    q = rng.integers(-127, 128, (8, 64), dtype=np.int8)
+    sc = rng.uniform(1e-4, 4e-4, (8, 2)).astype(np.float16)
+    blocks = q8_0_blocks(q, sc)
+    got = O.to_f32(blocks, 3).reshape(8, 64)
+    assert np.array_equal(got, np.repeat(sc.astype(np.float32), 32, axis=1) * q)
+    try:
+        from gguf import GGMLQuantizationType, quants
+    except Exception:
+        pytest.skip("gguf python package not importable")
+    deq = quants.dequantize(blocks.reshape(-1, 34), GGMLQuantizationType.Q8_0).reshape(8, 64)
+    assert np.array_equal(got, deq.astype(np.float32))
+
+
+def test_sin_cos_tables(L, O):
+    s, c = O.build_sin_cos(64, 128, 5e5)
+    s2, c2 = L.build_sin_cos(64, 128, 5e5)
+    assert np.array_equal(s, s2) and np.array_equal(c, c2)
+    i = np.arange(64, dtype=np.float32)
+    inv = np.power(np.float32(5e5), -(2 * i) / np.float32(128)).astype(np.float32)
+    ang = (np.arange(64, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    assert np.abs(s - np.sin(ang.astype(np.float64))).max() < 2e-5  # numpy pow vs powf differ by an ulp of the angle
+    assert s[0].max() == 0 and c[0].min() == 1
+
+
+def test_ops_against_numpy(O):
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((3, 96)).astype(np.float32)
+    w = rng.standard_normal(96).astype(np.float32)
+    want = x * w / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-5)
+    assert np.abs(O.rms_norm(x, w, 1e-5, 2) - want).max() < 1e-5
+    W = rng.standard_normal((40, 96)).astype(np.float32)
+    r = rng.standard_normal((3, 40)).astype(np.float32)
+    assert np.abs(O.linear(x, W, r, 2) - (x.astype(np.float64) @ W.T + r)).max() < 1e-4
+    g, u = rng.standard_normal((2, 50)).astype(np.float32), rng.standard_normal((2, 50)).astype(np.float32)
+    assert np.abs(O.swiglu(g, u, 2) - g / (1 + np.exp(-g.astype(np.float64))) * u).max() < 1e-6
+    # rope: adjacent pairs
+    s, c = O.build_sin_cos(16, 8, 1e4)
+    xr = rng.standard_normal((2, 16)).astype(np.float32)
+    y = O.rope(xr, 2, 8, [3, 7], s, c, 2)
+    for t, p in enumerate([3, 7]):
+        for h in range(2):
+            for i in range(4):
+                a, b = xr[t, h * 8 + 2 * i], xr[t, h * 8 + 2 * i + 1]
+                assert abs(y[t, h * 8 + 2 * i] - (a * c[p, i] - b * s[p, i])) < 1e-6
+                assert abs(y[t, h * 8 + 2 * i + 1] - (a * s[p, i] + b * c[p, i])) < 1e-6
+
+
+def test_attention_causal_gqa(O):
+    rng = np.random.default_rng(6)
+    nh, nkvh, dh, pos, seq = 4, 2, 8, 5, 3
+    q = rng.standard_normal((seq, nh * dh)).astype(np.float32)
+    kc = rng.standard_normal((pos + seq, nkvh * dh)).astype(np.float32)
+    vc = rng.standard_normal((pos + seq, nkvh * dh)).astype(np.float32)
+    got = O.attention(q, kc, vc, nh, nkvh, dh, pos, 2)
+    for t in range(seq):
+        for h in range(nh):
+            kv = h // (nh // nkvh)
+            ctx = pos + t + 1
+            s = kc[:ctx, kv * dh:(kv + 1) * dh].astype(np.float64) @ q[t, h * dh:(h + 1) * dh] / np.sqrt(dh)
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            want = p @ vc[:ctx, kv * dh:(kv + 1) * dh]
+            assert np.abs(got[t, h * dh:(h + 1) * dh] - want).max() < 1e-5
+
+
+def test_argmax_lowest_index_on_ties(O):
+    a = np.array([0.5, 2.0, -1.0, 2.0, 2.0], np.float32)
+    assert O.argmax(a) == (1, 2.0)
+
+
+def test_sample_semantics(O):
+    """The restated sampler: threshold = random * min(top_p * total, prefix[top_k - 1])."""
+    lg = np.array([1.0, 3.0, 2.0, 3.0, 0.0], np.float32)  # sorted: idx1(3), idx3(3), idx2(2), idx0(1), idx4(0)
+    w = np.exp(np.array([0.0, 0.0, -1.0, -2.0, -3.0]))
+    cum = np.cumsum(w)
+    assert O.sample(lg, 0.0, 1.0, 1.0, 5)[0] == 1            # smallest threshold -> first entry
+    assert O.sample(lg, 0.999, 1.0, 1.0, 5)[0] == 4          # whole mass -> last entry
+    assert O.sample(lg, 0.999, 1.0, 1.0, 2)[0] == 3          # top_k = 2 caps at prefix[1]
+    thr = 0.5 * min(0.6 * cum[-1], cum[4])
+    want = [1, 3, 2, 0, 4][int(np.searchsorted(cum, thr))]
+    assert O.sample(lg, 0.5, 1.0, 0.6, 5)[0] == want
+    # temperature sharpens: with T -> small everything lands on the maxima
+    assert O.sample(lg, 0.4, 0.01, 1.0, 5)[0] == 1
+    assert O.sample(lg, 0.6, 0.01, 1.0, 5)[0] == 3
