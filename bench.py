@@ -188,11 +188,7 @@ def main():
     steps_total = args.warmup + args.steps
     nctx = max(lengths) + 2 * steps_total + 8
     nctx = (nctx + 63) // 64 * 64
-    weights = L.synth_weights_torch(cfg, seed=0, device=dev)
-    if world > 1:
-        for k in list(weights):
-            if k[1] in L.LINEAR_KINDS:
-                pass  # sliced inside load_model
+    weights = L.iter_synth_weights_torch(cfg, seed=0, device=dev)  # one tensor at a time, sliced per rank
     kv_tokens = sum(n + 2 * steps_total + 64 for n in lengths)
     kv_bytes = kv_tokens * cfg.kv_bytes_per_token(world) + (64 << 20)
     ctx = L.load_model(cfg, weights, device=local_rank, kv_bytes=kv_bytes, tp_rank=rank, tp_size=world, comm=comm,

@@ -119,6 +119,7 @@ _SIGNATURES = {
     "lcu_sample_rows_workspace_size": (C.c_size_t, [C.c_int, C.c_size_t]),
     "lcu_op_sample_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p, C.c_void_p,
                                      C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "lcu_argmax_rows_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_int, C.c_void_p]),
     "lcu_comm_unique_id": (C.c_int, [C.c_void_p]),
     "lcu_comm_init_rank": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "lcu_comm_destroy": (C.c_int, [C.c_void_p]),
@@ -332,5 +333,6 @@ def _view(address, n_elems, dt, device):
     return t.view(torch_dtype(dt))
 
 
-from .model import CONFIGS, ModelConfig, load_model, synth_weights_numpy, synth_weights_torch  # noqa: E402,F401
+from .model import (CONFIGS, ModelConfig, iter_synth_weights_torch, load_model, synth_weights_numpy,  # noqa: E402,F401
+                    synth_weights_torch, tp_slice_numpy)
 from .host import Service, Session, generate  # noqa: E402,F401

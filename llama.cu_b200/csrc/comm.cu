@@ -24,6 +24,7 @@ struct Nccl {
     int (*CommInitRank)(void **, int, NcclId, int) = nullptr;
     int (*CommDestroy)(void *) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*Broadcast)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
 };
 Nccl g_nccl;
@@ -48,8 +49,9 @@ int load_nccl() {
     n.CommInitRank = reinterpret_cast<decltype(n.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
     n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
     n.AllReduce = reinterpret_cast<decltype(n.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+    n.Broadcast = reinterpret_cast<decltype(n.Broadcast)>(dlsym(lib, "ncclBroadcast"));
     n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
-    if (!n.GetUniqueId || !n.CommInitRank || !n.CommDestroy || !n.AllReduce) {
+    if (!n.GetUniqueId || !n.CommInitRank || !n.CommDestroy || !n.AllReduce || !n.Broadcast) {
         set_error("NCCL library lacks an expected symbol");
         return LCU_ERR_COMM;
     }
@@ -78,6 +80,19 @@ int comm_all_reduce(void *comm, void *y, const void *x, size_t count, int dt, cu
     }
     int e = g_nccl.AllReduce(x, y, count, nt, 0, comm, s);
     if (e) return nccl_fail(e, "ncclAllReduce");
+    return LCU_OK;
+}
+
+// == `comm.broadcast(tok_buf, None, 0, stream)` (llama.cu/src/exec/group.rs:114-115)
+int comm_broadcast(void *comm, void *buf, size_t bytes, int root, cudaStream_t s) {
+    if (!comm) {
+        set_error("broadcast: no communicator");
+        return LCU_ERR_COMM;
+    }
+    int rc = load_nccl();
+    if (rc) return rc;
+    int e = g_nccl.Broadcast(buf, buf, bytes, 0 /* ncclInt8 */, root, comm, s);
+    if (e) return nccl_fail(e, "ncclBroadcast");
     return LCU_OK;
 }
 

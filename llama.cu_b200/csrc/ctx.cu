@@ -545,9 +545,18 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
 
     // token feedback, then the embedding gather
     if (r.n_fast > 0) {
-        rc = op_fast_embedding(tokens, c->pre_pairs, fast_map, r.n_fast, s, false);
-        if (rc) return rc;
-        ++launches;
+        // the sampled ids live on the lead rank only: it patches the token buffer and, under
+        // tensor parallelism, broadcasts it (FastEmbedding then share_inputs, exec/engine.rs:258-274)
+        if (c->tp_rank == 0) {
+            rc = op_fast_embedding(tokens, c->pre_pairs, fast_map, r.n_fast, s, false);
+            if (rc) return rc;
+            ++launches;
+        }
+        if (c->tp_size > 1) {
+            rc = comm_broadcast(c->comm, tokens, (size_t)r.n_tok * 4, 0, s);
+            if (rc) return rc;
+            ++launches;
+        }
     }
     rc = op_embedding(c->x, c->embd, tokens, r.n_tok, (size_t)d.d * 2, s, r.n_fast > 0);
     if (rc) return rc;
@@ -695,7 +704,7 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
     const lcu_model_desc &d = c->desc;
     LCU_REQUIRE(d.vocab % 2 == 0, "step: vocab %d must be even", d.vocab);
     if (!c->pool) { set_error("step: no KV pool"); return LCU_ERR_STATE; }
-    if (!c->embd || !c->out_norm || !c->lm_head) { set_error("step: embedding / output weights missing"); return LCU_ERR_STATE; }
+    if (!c->embd || (c->tp_rank == 0 && (!c->out_norm || !c->lm_head))) { set_error("step: embedding / output weights missing"); return LCU_ERR_STATE; }
     for (int l = 0; l < d.n_layers; ++l) {
         const LayerWeights &W = c->layers[l];
         if (!W.attn_norm || !W.qkv || !W.o || !W.ffn_norm || !W.gate_up || !W.down) {

@@ -18,5 +18,6 @@ int op_add(void *y, int sny, int sdy, const void *x, int snx, int sdx, const voi
 
 // NCCL through dlopen (comm.cu)
 int comm_all_reduce(void *comm, void *y, const void *x, size_t count, int dt, cudaStream_t s);
+int comm_broadcast(void *comm, void *buf, size_t bytes, int root, cudaStream_t s);
 
 }  // namespace lcu

@@ -121,6 +121,12 @@ def synth_weights_numpy(cfg, seed=0):
 def synth_weights_torch(cfg, seed=0, device="cuda:0"):
     """Same distribution generated on the device (Philox), for shapes too large to draw on the host.
     Returns {(layer, kind): tensor}; Q8_0 weights come as one uint8 tensor in the plane layout."""
+    return dict(iter_synth_weights_torch(cfg, seed, device))
+
+
+def iter_synth_weights_torch(cfg, seed=0, device="cuda:0"):
+    """Generator form of synth_weights_torch: yields ((layer, kind), tensor) one tensor at a time, so a
+    tensor-parallel rank can slice each full tensor and drop it before the next one is drawn."""
     import torch
     g = torch.Generator(device=device)
     g.manual_seed(seed)
@@ -143,17 +149,35 @@ def synth_weights_torch(cfg, seed=0, device="cuda:0"):
         buf[rows * cols:] = sc.to(torch.float16).view(torch.uint8)
         return buf
 
-    w = {(-1, W_EMBD): dense(sh[W_EMBD])}
+    yield (-1, W_EMBD), dense(sh[W_EMBD])
     for l in range(cfg.n_layers):
-        w[(l, W_ATTN_NORM)] = torch.ones(cfg.d, dtype=tdt, device=device)
-        w[(l, W_QKV)] = linear(sh[W_QKV])
-        w[(l, W_O)] = linear(sh[W_O])
-        w[(l, W_FFN_NORM)] = torch.ones(cfg.d, dtype=tdt, device=device)
-        w[(l, W_GATE_UP)] = linear(sh[W_GATE_UP])
-        w[(l, W_DOWN)] = linear(sh[W_DOWN])
-    w[(-1, W_OUT_NORM)] = torch.ones(cfg.d, dtype=tdt, device=device)
-    w[(-1, W_LM_HEAD)] = dense(sh[W_LM_HEAD])
-    return w
+        yield (l, W_ATTN_NORM), torch.ones(cfg.d, dtype=tdt, device=device)
+        yield (l, W_QKV), linear(sh[W_QKV])
+        yield (l, W_O), linear(sh[W_O])
+        yield (l, W_FFN_NORM), torch.ones(cfg.d, dtype=tdt, device=device)
+        yield (l, W_GATE_UP), linear(sh[W_GATE_UP])
+        yield (l, W_DOWN), linear(sh[W_DOWN])
+    yield (-1, W_OUT_NORM), torch.ones(cfg.d, dtype=tdt, device=device)
+    yield (-1, W_LM_HEAD), dense(sh[W_LM_HEAD])
+
+
+def tp_slice_numpy(cfg, kind, full, rank, tp):
+    """This rank's part of a full weight, as `TPAction::move_data` cuts it (llama.cu/src/load/mod.rs:86-99)
+    with `Distribution{start=rank, len=1, total=tp}`: q, k, v row blocks by heads; O and down input columns;
+    gate and up row blocks.  Other kinds are replicated."""
+    dh, nh_l, nkvh_l, di_l = cfg.dh, cfg.nh // tp, cfg.nkvh // tp, cfg.di // tp
+    if kind == W_QKV:
+        q0, k0, v0 = 0, cfg.nh * dh, (cfg.nh + cfg.nkvh) * dh
+        return np.concatenate([full[q0 + rank * nh_l * dh:q0 + (rank + 1) * nh_l * dh],
+                               full[k0 + rank * nkvh_l * dh:k0 + (rank + 1) * nkvh_l * dh],
+                               full[v0 + rank * nkvh_l * dh:v0 + (rank + 1) * nkvh_l * dh]])
+    if kind == W_O:
+        return np.ascontiguousarray(full[:, rank * nh_l * dh:(rank + 1) * nh_l * dh])
+    if kind == W_GATE_UP:
+        return np.concatenate([full[rank * di_l:(rank + 1) * di_l], full[cfg.di + rank * di_l:cfg.di + (rank + 1) * di_l]])
+    if kind == W_DOWN:
+        return np.ascontiguousarray(full[:, rank * di_l:(rank + 1) * di_l])
+    return full
 
 
 def load_model(cfg, weights, device=0, kv_bytes=None, tp_rank=0, tp_size=1, comm=None, page_tokens=0,
@@ -165,7 +189,8 @@ def load_model(cfg, weights, device=0, kv_bytes=None, tp_rank=0, tp_size=1, comm
     dev = f"cuda:{device}"
     ctx = Context(cfg.desc(page_tokens, max_tokens, max_seqs, nctx), device, tp_rank, tp_size, comm)
     lib = load_library()
-    for (layer, kind), w in weights.items():
+    items = weights.items() if isinstance(weights, dict) else weights
+    for (layer, kind), w in items:
         if isinstance(w, dict):  # Q8_0 from numpy: upload ggml blocks, repack on the device
             rows, cols = w["q"].shape
             blocks = torch.from_numpy(w["blocks"]).to(dev)
@@ -179,6 +204,8 @@ def load_model(cfg, weights, device=0, kv_bytes=None, tp_rank=0, tp_size=1, comm
         if tp_size > 1 and kind in LINEAR_KINDS:
             t = ctx.tp_slice(kind, t)
             torch.cuda.synchronize(device)
+        if tp_size > 1 and tp_rank != 0 and kind == W_LM_HEAD:
+            continue  # the head runs on the lead rank only
         ctx.set_weight(max(layer, 0), kind, t)
     if kv_bytes is None:
         kv_bytes = 64 * ctx.page_bytes
