@@ -228,6 +228,21 @@ LCU_API int lcu_op_sample_rows(lcu_kv_pair *out, lcu_kv_pair *out_copy, const vo
                        const lcu_sample_args *args_dev, const float *randoms_dev, int dt, void *workspace,
                        size_t workspace_len, lcu_stream_t s);
 
+/* Arg-max of every row with NO workspace argument and no allocation of any kind.
+ * (No counterpart in the reference, whose sampler always takes a caller workspace.)
+ * For hosts that can neither pass scratch memory nor let the library allocate it — a serving
+ * loop that must keep cudaMalloc (a device-wide synchronisation) off its hot path, a host
+ * whose device memory belongs to an external pool, code already inside a stream capture.
+ * The partial results live in a fixed 64 KiB array inside the library image (held by every
+ * GPU that loads the library until the process exits), which limits the problem to
+ * rows * ceil(n / 4096) <= 8192; larger calls fail with LCU_ERR_INVALID and a message.
+ * The FIRST call on each device also looks up the array's device address; make that call
+ * with the device current and before starting any stream capture.  All calls share the one
+ * array: calls that overlap on the GPU (different streams, no ordering) race and give
+ * undefined results; nothing in it has to start at zero, so back-to-back calls on one
+ * stream need no clearing.  Same result as lcu_op_sample_rows with args_dev == NULL. */
+LCU_API int lcu_argmax_rows_noalloc(lcu_kv_pair *out, const void *logits, int rows, size_t n, int dt, lcu_stream_t s);
+
 /* ------------------------------------------------------------------ collectives set-up
  * Thin wrappers over the NCCL library found at run time == `CommunicatorGroup::new`
  * (exec/engine.rs:86), one process per GPU instead of one thread per GPU. */

@@ -16,6 +16,8 @@
 // ascending index, which is exactly the order a stable descending sort produces.
 #include "sample.cuh"
 
+#include <mutex>
+
 namespace lcu {
 
 template <class T> __device__ __forceinline__ float bits_to_f(uint16_t b);
@@ -325,3 +327,50 @@ int sample_rows(lcu_kv_pair *out, lcu_kv_pair *out_copy, const void *logits, int
 }
 
 }  // namespace lcu
+
+// ------------------------------------------------------------------ arg-max without any allocation
+//
+// Some hosts cannot hand this library a workspace and cannot let it allocate one: a serving
+// loop that must never call cudaMalloc on its hot path (the call synchronises the whole
+// device and would stall every other stream), a host whose device memory is owned
+// entirely by an external pool it may not touch from here, or code that is already
+// recording a stream capture, where allocation is not permitted.  For them the partial
+// (value, index) pairs of the two-stage arg-max live in a fixed array inside the library
+// image.  Every GPU that loads the library carries this array until the process exits.
+namespace lcu {
+constexpr size_t NOALLOC_SLOTS = 8192;  // rows x ceil(n / ARGMAX_CHUNK) partial pairs at most
+static __device__ __align__(256) unsigned char g_noalloc_scratch[2 * NOALLOC_SLOTS * 4 + 512];
+}  // namespace lcu
+
+extern "C" int lcu_argmax_rows_noalloc(lcu_kv_pair *out, const void *logits, int rows, size_t n, int dt,
+                                       lcu_stream_t stream) {
+    using namespace lcu;
+    LCU_REQUIRE(out && logits, "argmax_rows_noalloc: null argument");
+    LCU_REQUIRE(rows >= 1 && n >= 1, "argmax_rows_noalloc: rows = %d, n = %zu", rows, n);
+    size_t slots = (size_t)rows * ((n + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK);
+    if (slots > NOALLOC_SLOTS || argmax_workspace_bytes(rows, n) > sizeof(g_noalloc_scratch)) {
+        set_error("argmax_rows_noalloc: %d rows of %zu logits need %zu partial slots, the built-in scratch holds %zu "
+                  "(use lcu_op_sample_rows with a caller workspace for larger problems)",
+                  rows, n, slots, NOALLOC_SLOTS);
+        return LCU_ERR_INVALID;
+    }
+    // The array's name is only a host-side handle; its device address is looked up once per
+    // device, with that device current, and kept.
+    static std::mutex mu;
+    static void *addr[64] = {nullptr};
+    int dev = 0;
+    LCU_CHECK_CUDA(cudaGetDevice(&dev));
+    LCU_REQUIRE(dev >= 0 && dev < 64, "argmax_rows_noalloc: device index %d out of range", dev);
+    void *ws = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!addr[dev]) {
+            void *p = nullptr;
+            LCU_CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            addr[dev] = p;
+        }
+        ws = addr[dev];
+    }
+    return sample_rows(out, nullptr, logits, rows, n, nullptr, nullptr, dt, ws, sizeof(g_noalloc_scratch), as_stream(stream),
+                       false, false);
+}
