@@ -169,6 +169,16 @@ LCU_API int lcu_device_status(lcu_ctx *ctx, lcu_stream_t stream, uint32_t *statu
 /* 1 = replay decode rounds from a captured CUDA graph (default), 0 = launch eagerly
  * == the reference's `--no-cuda-graph` switch (xtask/src/main.rs:45-73). */
 LCU_API int lcu_set_cuda_graph(lcu_ctx *ctx, int enabled);
+/* 1 = run decode rounds of up to 4 sequences (single GPU, f16/bf16 weights) as one persistent
+ * whole-step kernel, 0 = use the kernel-per-operator path (default).  The reference has no
+ * counterpart: it launches one kernel or library call per operator (exec/step.rs:101-138). */
+LCU_API int lcu_set_megakernel(lcu_ctx *ctx, int enabled);
+/* Cycle counters of the persistent kernel (SM clocks spent by CTA 0, summed over the steps since the
+ * last call): out16[0..5] tile loops of the QKV / attention / O / gate|up / down / head phases,
+ * [8] grid barriers, [9] activation prologues, [10] waits for weight tiles, [11] steps counted.
+ * Synchronises the device, copies and clears the counters, then switches counting on or off.
+ * (A measurement aid without counterpart in the reference; out16 may be NULL.) */
+LCU_API int lcu_profile_counters(lcu_ctx *ctx, int enable, long long *out16);
 /* Number of kernels of this library launched by the last lcu_step. */
 LCU_API int lcu_last_launch_count(const lcu_ctx *ctx);
 /* Algorithmic HBM bytes of the last round (weights streamed + KV read), for rooflines. */

@@ -96,6 +96,8 @@ _SIGNATURES = {
     "lcu_hidden": (C.c_void_p, [C.c_void_p]),
     "lcu_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
     "lcu_set_cuda_graph": (C.c_int, [C.c_void_p, C.c_int]),
+    "lcu_set_megakernel": (C.c_int, [C.c_void_p, C.c_int]),
+    "lcu_profile_counters": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_last_launch_count": (C.c_int, [C.c_void_p]),
     "lcu_last_step_bytes": (C.c_double, [C.c_void_p]),
     "lcu_op_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
@@ -309,6 +311,15 @@ class Context:
 
     def set_cuda_graph(self, enabled):
         check(self.lib.lcu_set_cuda_graph(self.h, int(enabled)))
+
+    def profile_counters(self, enable=True):
+        """Reads and clears the persistent kernel's cycle counters (see lcu_profile_counters)."""
+        out = (C.c_longlong * 16)()
+        check(self.lib.lcu_profile_counters(self.h, int(enable), out))
+        return list(out)
+
+    def set_megakernel(self, enabled):
+        check(self.lib.lcu_set_megakernel(self.h, int(enabled)))
 
     @property
     def last_launch_count(self):

@@ -65,6 +65,31 @@ template <> struct Act<__nv_bfloat16> {
 // output in that type, so fused kernels round at the same places
 template <class T> __device__ __forceinline__ float round_act(float v) { return Act<T>::to_f(Act<T>::from_f(v)); }
 
+// acc += a.lo * b.lo; acc += a.hi * b.hi for two packed 16-bit floats per operand, with the
+// sm_100 mixed-precision FMA (f16/bf16 inputs, f32 accumulate, one rounding): the same value
+// as converting both inputs to f32 and calling fmaf, without the two conversions.
+template <class T> __device__ __forceinline__ float fma2_mixed(uint32_t a, uint32_t b, float acc);
+template <> __device__ __forceinline__ float fma2_mixed<__half>(uint32_t a, uint32_t b, float acc) {
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
+        " fma.rn.f32.f16 %0, al, bl, %0;\n fma.rn.f32.f16 %0, ah, bh, %0;\n}"
+        : "+f"(acc) : "r"(a), "r"(b));
+    return acc;
+}
+template <> __device__ __forceinline__ float fma2_mixed<__nv_bfloat16>(uint32_t a, uint32_t b, float acc) {
+    asm("{\n .reg .b16 al, ah, bl, bh;\n mov.b32 {al, ah}, %1;\n mov.b32 {bl, bh}, %2;\n"
+        " fma.rn.f32.bf16 %0, al, bl, %0;\n fma.rn.f32.bf16 %0, ah, bh, %0;\n}"
+        : "+f"(acc) : "r"(a), "r"(b));
+    return acc;
+}
+// dot product of 8 + 8 packed values accumulated in element order 0..7
+template <class T> __device__ __forceinline__ float dot8_mixed(const uint4 &w, const uint4 &x, float acc) {
+    acc = fma2_mixed<T>(w.x, x.x, acc);
+    acc = fma2_mixed<T>(w.y, x.y, acc);
+    acc = fma2_mixed<T>(w.z, x.z, acc);
+    acc = fma2_mixed<T>(w.w, x.w, acc);
+    return acc;
+}
+
 // ------------------------------------------------------------------ memory access
 // 128-bit streaming load for data read exactly once per step (weights): no L1 allocation,
 // read-only path.

@@ -12,6 +12,7 @@
 #include "attention.cuh"
 #include "common.cuh"
 #include "gemv.cuh"
+#include "megakernel.cuh"
 #include "ops.cuh"
 #include "sample.cuh"
 
@@ -109,6 +110,20 @@ struct lcu_ctx {
     bool desc_used[RING] = {false, false, false, false};
     int ring_idx = 0;
 
+    // persistent whole-step kernel (1..4 sequences, single GPU, f16/bf16 weights)
+    bool use_megakernel = false;  // opt-in (lcu_set_megakernel): not yet faster than the kernel-per-operator path
+    bool mk_ok[3] = {false, false, false};   // for 1, 2, 4 tokens
+    size_t mk_smem[3] = {0, 0, 0};
+    int mk_stages[3] = {0, 0, 0}, mk_xbytes[3] = {0, 0, 0}, mk_pbytes[3] = {0, 0, 0};
+    MkPhase *mk_phases_dev = nullptr;
+    int mk_n_phases = 0;
+    bool mk_phases_valid = false;
+    float *mk_attn_part = nullptr, *mk_best_v = nullptr;
+    uint32_t *mk_best_i = nullptr;
+    unsigned *mk_grid_bar = nullptr;
+    long long *mk_prof = nullptr;
+    bool mk_profile = false;
+
     bool use_graph = true;
     std::map<std::vector<int>, StepGraph> graphs;
     int last_launches = 0;
@@ -166,6 +181,7 @@ static bool is_linear_kind(int kind) {
 
 // captured graphs hold weight pointers: any change of registered memory drops them
 static void drop_graphs(lcu_ctx *c) {
+    c->mk_phases_valid = false;
     for (auto &g : c->graphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     c->graphs.clear();
@@ -285,7 +301,12 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     c->sample_ws_bytes = align256(sample_workspace_bytes(c->max_seqs, (size_t)d.vocab));
     size_t sz_pairs = align256((size_t)c->max_tokens * sizeof(lcu_kv_pair));
     c->desc_cap = align256(desc_layout(c->max_tokens, c->max_seqs, c->pt_stride).total);
-    size_t total = sz_x + 2 * sz_q + sz_act + sz_logits + sz_attn + c->sample_ws_bytes + sz_pairs + 256 + c->desc_cap;
+    const int grid = sm_count();
+    size_t sz_mk_part = align256((size_t)4 * c->nh_l * 16 * (d.dh + 2) * 4);
+    size_t sz_mk_best = align256((size_t)grid * 4 * 4);
+    size_t sz_mk_phases = align256((size_t)(d.n_layers * 5 + 1) * sizeof(MkPhase));
+    size_t total = sz_x + 2 * sz_q + sz_act + sz_logits + sz_attn + c->sample_ws_bytes + sz_pairs + 512 + c->desc_cap +
+                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases;
     cudaError_t e = cudaMalloc(&c->arena, total);
     if (e != cudaSuccess) {
         delete c;
@@ -301,8 +322,15 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     c->attn_scratch = p; p += sz_attn;
     c->sample_ws = p; p += c->sample_ws_bytes;
     c->pre_pairs = reinterpret_cast<lcu_kv_pair *>(p); p += sz_pairs;
-    c->dev_status = reinterpret_cast<uint32_t *>(p); p += 256;
-    c->desc_dev = p;
+    c->dev_status = reinterpret_cast<uint32_t *>(p);
+    c->mk_grid_bar = reinterpret_cast<unsigned *>(p + 128);
+    c->mk_prof = reinterpret_cast<long long *>(p + 256);
+    p += 512;
+    c->desc_dev = p; p += c->desc_cap;
+    c->mk_attn_part = reinterpret_cast<float *>(p); p += sz_mk_part;
+    c->mk_best_v = reinterpret_cast<float *>(p); p += sz_mk_best;
+    c->mk_best_i = reinterpret_cast<uint32_t *>(p); p += sz_mk_best;
+    c->mk_phases_dev = reinterpret_cast<MkPhase *>(p);
     for (int i = 0; i < lcu_ctx::RING; ++i) {
         e = cudaMallocHost(reinterpret_cast<void **>(&c->desc_host[i]), c->desc_cap);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->desc_event[i], cudaEventDisableTiming);
@@ -326,6 +354,19 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
         if (rc) {
             lcu_ctx_destroy(c);
             return rc;
+        }
+        // the persistent whole-step kernel: single GPU, unquantised weights, shapes it can tile
+        int R, KC, nkc;
+        bool tiles_ok = !q8 && tp_size == 1 && mk_plan_tiles(d.d, &R, &KC, &nkc) && mk_plan_tiles(c->qd, &R, &KC, &nkc) &&
+                        mk_plan_tiles(c->di_l, &R, &KC, &nkc) && d.vocab % 2 == 0;
+        int max_in = d.d > c->qd ? d.d : c->qd;
+        if (c->di_l > max_in) max_in = c->di_l;
+        for (int i = 0; i < 3 && tiles_ok; ++i) {
+            int nt = 1 << i;
+            if (nt > c->max_seqs && i > 0) break;
+            c->mk_smem[i] = mk_smem_bytes(nt, max_in, c->nh_l, c->nkvh_l, d.dh, &c->mk_stages[i], &c->mk_xbytes[i], &c->mk_pbytes[i]);
+            if (!c->mk_smem[i] || nt * c->nkvh_l > sm_count()) continue;
+            c->mk_ok[i] = mk_prepare(c->dt, nt, c->mk_smem[i]) == LCU_OK;
         }
     }
     *out = c;
@@ -497,6 +538,22 @@ int lcu_set_cuda_graph(lcu_ctx *c, int enabled) {
     c->use_graph = enabled != 0;
     return LCU_OK;
 }
+int lcu_set_megakernel(lcu_ctx *c, int enabled) {
+    LCU_REQUIRE(c, "set_megakernel: null context");
+    c->use_megakernel = enabled != 0;
+    return LCU_OK;
+}
+int lcu_profile_counters(lcu_ctx *c, int enable, long long *out16) {
+    LCU_REQUIRE(c, "profile_counters: null context");
+    LCU_CHECK_CUDA(cudaDeviceSynchronize());
+    if (out16) LCU_CHECK_CUDA(cudaMemcpy(out16, c->mk_prof, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
+    LCU_CHECK_CUDA(cudaMemset(c->mk_prof, 0, 16 * sizeof(long long)));
+    if (c->mk_profile != (enable != 0)) {
+        c->mk_profile = enable != 0;
+        drop_graphs(c);
+    }
+    return LCU_OK;
+}
 int lcu_last_launch_count(const lcu_ctx *c) { return c ? c->last_launches : 0; }
 double lcu_last_step_bytes(const lcu_ctx *c) { return c ? c->last_bytes : 0.0; }
 const void *lcu_logits(const lcu_ctx *c) { return c ? c->logits : nullptr; }
@@ -514,6 +571,34 @@ int lcu_device_status(lcu_ctx *c, lcu_stream_t stream, uint32_t *status_out) {
 // ------------------------------------------------------------------ the round
 
 namespace {
+
+// (Re)builds the device-side phase list of the persistent kernel from the registered weights.
+int mk_build_phases(lcu_ctx *c) {
+    if (c->mk_phases_valid) return LCU_OK;
+    const lcu_model_desc &d = c->desc;
+    std::vector<MkPhase> ph;
+    auto weight_phase = [&](int kind, int layer, const void *w, const void *norm, int in, int out, int swiglu_di) {
+        MkPhase p{};
+        p.w = w; p.norm_w = norm; p.kind = kind; p.layer = layer; p.in = in; p.n_pairs = out / 2; p.swiglu_di = swiglu_di;
+        mk_plan_tiles(in, &p.R, &p.KC, &p.n_kc);
+        ph.push_back(p);
+    };
+    for (int l = 0; l < d.n_layers; ++l) {
+        const LayerWeights &W = c->layers[l];
+        weight_phase(MK_QKV, l, W.qkv, W.attn_norm, d.d, c->qd + 2 * c->kvd, 0);
+        MkPhase at{};
+        at.kind = MK_ATTN; at.layer = l;
+        ph.push_back(at);
+        weight_phase(MK_O, l, W.o, nullptr, c->qd, d.d, 0);
+        weight_phase(MK_GATE_UP, l, W.gate_up, W.ffn_norm, d.d, 2 * c->di_l, c->di_l);
+        weight_phase(MK_DOWN, l, W.down, nullptr, c->di_l, d.d, 0);
+    }
+    weight_phase(MK_HEAD, d.n_layers, c->lm_head, c->out_norm, d.d, d.vocab, 0);
+    LCU_CHECK_CUDA(cudaMemcpy(c->mk_phases_dev, ph.data(), ph.size() * sizeof(MkPhase), cudaMemcpyHostToDevice));
+    c->mk_n_phases = (int)ph.size();
+    c->mk_phases_valid = true;
+    return LCU_OK;
+}
 
 struct Round {
     int n_tok, n_req, n_fast;
@@ -692,6 +777,62 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     return LCU_OK;
 }
 
+// One decode round (1..4 sequences, one token each) as ONE persistent cooperative kernel.
+int enqueue_round_mk(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t s, int *count) {
+    const lcu_model_desc &d = c->desc;
+    const int vi = r.n_tok <= 1 ? 0 : (r.n_tok == 2 ? 1 : 2);
+    unsigned char *D = c->desc_dev;
+    MkArgs a{};
+    a.phases = c->mk_phases_dev;
+    a.n_phases = c->mk_n_phases;
+    a.n_tok = r.n_tok;
+    a.d = d.d; a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.nh = c->nh_l; a.nkvh = c->nkvh_l; a.di = c->di_l; a.vocab = d.vocab;
+    a.eps = d.eps;
+    a.norm_f32 = d.norm_dtype == LCU_F32;
+    a.tokens = reinterpret_cast<uint32_t *>(D + r.L.tokens);
+    a.pos = reinterpret_cast<const uint32_t *>(D + r.L.pos);
+    a.fast_map = reinterpret_cast<const uint32_t *>(D + r.L.fast_map);
+    a.n_fast = r.n_fast;
+    a.pre_pairs_in = c->pre_pairs;
+    a.page_table = reinterpret_cast<const int32_t *>(D + r.L.page_table);
+    a.pt_stride = c->pt_stride;
+    a.embd = c->embd;
+    a.sin_t = c->sin_t; a.cos_t = c->cos_t;
+    a.kv_pool = c->pool;
+    a.geom = c->geom;
+    a.x = c->x; a.q = c->q; a.act = c->act; a.logits = c->logits;
+    a.attn_part = c->mk_attn_part;
+    a.s_max = mk_splits(sm_count(), r.n_tok <= 1 ? 1 : (r.n_tok == 2 ? 2 : 4), c->nkvh_l);
+    a.head_best_v = c->mk_best_v;
+    a.head_best_i = c->mk_best_i;
+    a.out = out_dev;
+    a.out_copy = c->pre_pairs;
+    a.grid_bar = c->mk_grid_bar;
+    a.status = c->dev_status;
+    a.prof = c->mk_profile ? c->mk_prof : nullptr;
+    a.n_stages = c->mk_stages[vi];
+    {
+        static const int l2_ahead = getenv("LCU_MK_L2_AHEAD") ? atoi(getenv("LCU_MK_L2_AHEAD")) : 0;
+        a.l2_ahead = l2_ahead;
+    }
+    a.smem_x_bytes = c->mk_xbytes[vi];
+    a.smem_part_bytes = c->mk_pbytes[vi];
+    LCU_CHECK_CUDA(cudaMemsetAsync(c->mk_grid_bar, 0, sizeof(unsigned), s));
+    int rc = mk_launch(a, c->dt, c->mk_smem[vi], s);
+    if (rc) return rc;
+    int launches = 1;
+    if (r.any_sampling) {  // rows that sample are redone from the logits; arg-max rows keep their pair
+        const lcu_sample_args *args = reinterpret_cast<const lcu_sample_args *>(D + r.L.args);
+        const float *randoms = reinterpret_cast<const float *>(D + r.L.randoms);
+        rc = sample_rows(out_dev, c->pre_pairs, c->logits, r.n_req, (size_t)d.vocab, args, randoms, c->dt, c->sample_ws,
+                         c->sample_ws_bytes, s, false, true);
+        if (rc) return rc;
+        launches += 3;
+    }
+    *count = launches;
+    return LCU_OK;
+}
+
 }  // namespace
 
 extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_req *reqs, const uint32_t *tokens,
@@ -807,21 +948,27 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
 
     // decode rounds replay a captured graph; everything else (and stream 0) runs eagerly.
     // NCCL collectives are captured like any other node (exec/step.rs:82-86).
+    const int mk_vi = n_tok <= 1 ? 0 : (n_tok == 2 ? 1 : 2);
+    const bool use_mk = c->use_megakernel && decode_only && n_tok <= 4 && c->tp_size == 1 && c->mk_ok[mk_vi];
+    if (use_mk) {
+        rc = mk_build_phases(c);
+        if (rc) return rc;
+    }
     bool graph_ok = c->use_graph && decode_only && s != nullptr;
     if (!graph_ok) {
         int count = 0;
-        rc = enqueue_round(c, r, out_dev, s, &count);
+        rc = use_mk ? enqueue_round_mk(c, r, out_dev, s, &count) : enqueue_round(c, r, out_dev, s, &count);
         c->last_launches = count;
         return rc;
     }
     std::vector<int> key = {n_req, n_tok, n_fast, any_sampling ? 1 : 0, (int)((uintptr_t)out_dev & 0x7fffffff),
-                            (int)((uintptr_t)out_dev >> 31)};
+                            (int)((uintptr_t)out_dev >> 31), use_mk ? 1 : 0};
     auto it = c->graphs.find(key);
     if (it == c->graphs.end()) {
         cudaGraph_t graph = nullptr;
         LCU_CHECK_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         int count = 0;
-        rc = enqueue_round(c, r, out_dev, s, &count);
+        rc = use_mk ? enqueue_round_mk(c, r, out_dev, s, &count) : enqueue_round(c, r, out_dev, s, &count);
         cudaError_t e = cudaStreamEndCapture(s, &graph);
         if (rc) {
             if (graph) cudaGraphDestroy(graph);

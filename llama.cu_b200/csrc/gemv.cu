@@ -28,10 +28,6 @@
 
 namespace lcu {
 
-__device__ __forceinline__ float swiglu_act(float gate, float up) {
-    return gate * __fdividef(1.f, 1.f + expf(-gate)) * up;
-}
-
 // int8 -> f32 without I2F: bytes xor 0x80 become 0..255, placed in the mantissa of 2^23.
 __device__ __forceinline__ void q8x4_to_f32(uint32_t q, float f[4]) {
     uint32_t u = q ^ 0x80808080u;
@@ -45,61 +41,6 @@ template <class T>
 __device__ __forceinline__ void vec8_to_f32(const uint4 &v, float f[8]) {
     float2 a = Act<T>::to_f2(v.x), b = Act<T>::to_f2(v.y), c = Act<T>::to_f2(v.z), d = Act<T>::to_f2(v.w);
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-}
-
-template <class T>
-__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
-    T *y = reinterpret_cast<T *>(a.y);
-    switch (a.epilogue) {
-    case EPI_STORE: {
-        size_t r = (size_t)pair * 2;
-        y[(size_t)t * a.stride_y + r] = Act<T>::from_f(va);
-        y[(size_t)t * a.stride_y + r + 1] = Act<T>::from_f(vb);
-        break;
-    }
-    case EPI_RESIDUAL: {
-        size_t r = (size_t)pair * 2;
-        const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + r;
-        // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
-        uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
-        float2 rf = Act<T>::to_f2(rr);
-        *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = Act<T>::pack(va + rf.x, vb + rf.y);
-        break;
-    }
-    case EPI_ROPE_KV: {
-        int r = pair * 2;
-        // the qkv projection is materialised in the activation dtype before rope reads it
-        float xa = round_act<T>(va), xb = round_act<T>(vb);
-        int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
-        int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
-        int head = rr / a.dh, e = rr - head * a.dh;
-        uint32_t p = a.pos[t];
-        if (sect < 2) {
-            int half_dh = a.dh >> 1;
-            float sn = a.sin_t[(size_t)p * half_dh + (e >> 1)], cs = a.cos_t[(size_t)p * half_dh + (e >> 1)];
-            float ya = xa * cs - xb * sn, yb = xa * sn + xb * cs;
-            xa = ya;
-            xb = yb;
-        }
-        uint32_t packed = Act<T>::pack(xa, xb);
-        if (sect == 0) {
-            *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
-        } else {
-            int seq = a.tok_seq[t];
-            int page = a.page_table[(size_t)seq * a.pt_stride + (p >> a.geom.page_shift)];
-            int slot = p & (a.geom.page_tokens - 1);
-            size_t off = a.geom.block_off(page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
-            *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.kv_pool) + off) = packed;
-        }
-        break;
-    }
-    case EPI_SWIGLU: {
-        // gate = row pair, up = row pair + di, both materialised before swiglu reads them
-        float g = round_act<T>(va), u = round_act<T>(vb);
-        y[(size_t)t * a.stride_y + pair] = Act<T>::from_f(swiglu_act(g, u));
-        break;
-    }
-    }
 }
 
 template <class T, bool Q8, int NT, int KI, int RP>
@@ -232,19 +173,13 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
             int kv = (ks + KS * ki) * 32 + lane;
             if (kv < nvec) {
                 if constexpr (!Q8) {
-                    float xf[NT][8];
+                    uint4 xv[NT];
 #pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        vec8_to_f32<T>(reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in)[kv], xf[t]);
+                    for (int t = 0; t < NT; ++t) xv[t] = reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in)[kv];
 #pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        float wf[8];
-                        vec8_to_f32<T>(wreg[r][ki], wf);
+                    for (int r = 0; r < R; ++r)
 #pragma unroll
-                        for (int t = 0; t < NT; ++t)
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[r][t] = fmaf(wf[j], xf[t][j], acc[r][t]);
-                    }
+                        for (int t = 0; t < NT; ++t) acc[r][t] = dot8_mixed<T>(wreg[r][ki], xv[t], acc[r][t]);
                 } else {
                     float xf[NT][16];
 #pragma unroll

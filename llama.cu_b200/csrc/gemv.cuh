@@ -47,6 +47,69 @@ struct GemvArgs {
     int early_prefetch;  // 1 = first weight loads before griddepcontrol.wait
 };
 
+#ifdef __CUDACC__
+// ---- fused epilogue of one row pair for one token, shared by the GEMV and the batched kernel
+__device__ __forceinline__ float swiglu_act(float gate, float up) {
+    return gate * __fdividef(1.f, 1.f + expf(-gate)) * up;
+}
+
+template <class T>
+__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
+    T *y = reinterpret_cast<T *>(a.y);
+    switch (a.epilogue) {
+    case EPI_STORE: {
+        size_t r = (size_t)pair * 2;
+        y[(size_t)t * a.stride_y + r] = Act<T>::from_f(va);
+        y[(size_t)t * a.stride_y + r + 1] = Act<T>::from_f(vb);
+        break;
+    }
+    case EPI_RESIDUAL: {
+        size_t r = (size_t)pair * 2;
+        const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + r;
+        // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
+        uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
+        float2 rf = Act<T>::to_f2(rr);
+        *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = Act<T>::pack(va + rf.x, vb + rf.y);
+        break;
+    }
+    case EPI_ROPE_KV: {
+        int r = pair * 2;
+        // the qkv projection is materialised in the activation dtype before rope reads it
+        float xa = round_act<T>(va), xb = round_act<T>(vb);
+        int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
+        int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
+        int head = rr / a.dh, e = rr - head * a.dh;
+        uint32_t p = a.pos[t];
+        if (sect < 2) {
+            int half_dh = a.dh >> 1;
+            float sn = a.sin_t[(size_t)p * half_dh + (e >> 1)], cs = a.cos_t[(size_t)p * half_dh + (e >> 1)];
+            float ya = xa * cs - xb * sn, yb = xa * sn + xb * cs;
+            xa = ya;
+            xb = yb;
+        }
+        uint32_t packed = Act<T>::pack(xa, xb);
+        if (sect == 0) {
+            *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
+        } else {
+            int seq = a.tok_seq[t];
+            int page = a.page_table[(size_t)seq * a.pt_stride + (p >> a.geom.page_shift)];
+            int slot = p & (a.geom.page_tokens - 1);
+            size_t off = a.geom.block_off(page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
+            *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.kv_pool) + off) = packed;
+        }
+        break;
+    }
+    case EPI_SWIGLU: {
+        // gate = row pair, up = row pair + di, both materialised before swiglu reads them
+        float g = round_act<T>(va), u = round_act<T>(vb);
+        y[(size_t)t * a.stride_y + pair] = Act<T>::from_f(swiglu_act(g, u));
+        break;
+    }
+    }
+}
+
+#endif  // __CUDACC__
+
 // Enqueues one GEMV; dt = LCU_F16 / LCU_BF16.  pdl: launch with programmatic serialisation.
 int gemv_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
 // Prepares (attributes, occupancy) every variant used for this shape without launching.
