@@ -184,6 +184,39 @@ LCU_API int lcu_last_launch_count(const lcu_ctx *ctx);
 /* Algorithmic HBM bytes of the last round (weights streamed + KV read), for rooflines. */
 LCU_API double lcu_last_step_bytes(const lcu_ctx *ctx);
 
+/* ------------------------------------------------------------------ round builder (host only)
+ * == `EngineManager` (exec/engine_manager.rs:15-156): continuous batching — every running session
+ * takes part in every round; a new one contributes its whole prompt, a running one a placeholder
+ * token that the device replaces with its previous sample (`fast_map`).  Needs no GPU; `ctx` may be
+ * NULL when only lcu_engine_prepare is used. */
+typedef struct lcu_engine lcu_engine;
+typedef struct {
+    int32_t n_tok, n_req, n_fast, n_finished, n_overflow;
+} lcu_round_info;
+LCU_API int lcu_engine_create(lcu_ctx *ctx, uint32_t nctx, lcu_engine **out);
+LCU_API int lcu_engine_destroy(lcu_engine *e);
+/* == a new `Session{id, sample_args, cache}`; `seq` is its KV handle (lcu_seq_create); args NULL = ARG_MAX */
+LCU_API int lcu_engine_session_new(lcu_engine *e, int seq, const lcu_sample_args *args, uint64_t *id_out);
+/* == `Terminal::start` / `Command::Insert` (lib.rs:233-243): run `prompt` from the session's position for max_steps rounds */
+LCU_API int lcu_engine_start(lcu_engine *e, uint64_t id, const uint32_t *prompt, uint32_t n, int max_steps);
+LCU_API int lcu_engine_remove(lcu_engine *e, uint64_t id); /* == `Command::Remove` */
+LCU_API int lcu_engine_session_pos(const lcu_engine *e, uint64_t id, uint32_t *pos_out);
+LCU_API int lcu_engine_session_set_pos(lcu_engine *e, uint64_t id, uint32_t pos); /* cache.pos rollback (prefix reuse) */
+/* == `EngineManager::prepare` (exec/engine_manager.rs:72-130); arrays below stay valid until the next prepare */
+LCU_API int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info);
+LCU_API const uint32_t *lcu_engine_round_tokens(const lcu_engine *e);            /* n_tok */
+LCU_API const lcu_req *lcu_engine_round_reqs(const lcu_engine *e);               /* n_req */
+LCU_API const uint32_t *lcu_engine_round_fast_map(const lcu_engine *e);          /* n_fast pairs */
+LCU_API const lcu_sample_args *lcu_engine_round_sample_args(const lcu_engine *e); /* n_req */
+LCU_API const uint64_t *lcu_engine_round_output(const lcu_engine *e);            /* n_req session ids, output order */
+LCU_API const uint64_t *lcu_engine_round_finished(const lcu_engine *e);          /* n_finished */
+LCU_API const uint64_t *lcu_engine_round_overflow(const lcu_engine *e);          /* n_overflow */
+/* == `pos()` and `out_idx()` (exec/engine.rs:352-371) of the prepared round; either pointer may be NULL */
+LCU_API int lcu_engine_round_positions(const lcu_engine *e, uint32_t *pos_out, uint32_t *out_idx_out);
+/* One iteration of `Worker::lead`'s loop: prepare + lcu_step.  info->n_tok == 0: nothing to run. */
+LCU_API int lcu_engine_step(lcu_engine *e, lcu_stream_t stream, const float *randoms, lcu_kv_pair *out_dev,
+                            lcu_round_info *info);
+
 /* ------------------------------------------------------------------ operators
  * One entry point per `Operator::launch` implementation so a host can swap them in one
  * at a time behind `launch_nn_exec` (exec/step.rs:101-138).  dt = activation dtype. */

@@ -61,6 +61,10 @@ class Req(C.Structure):
     _fields_ = [("seq", C.c_int32), ("pos", C.c_uint32), ("len", C.c_uint32)]
 
 
+class RoundInfo(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_tok", "n_req", "n_fast", "n_finished", "n_overflow")]
+
+
 _lib = None
 
 
@@ -100,6 +104,23 @@ _SIGNATURES = {
     "lcu_profile_counters": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_last_launch_count": (C.c_int, [C.c_void_p]),
     "lcu_last_step_bytes": (C.c_double, [C.c_void_p]),
+    "lcu_engine_create": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]),
+    "lcu_engine_destroy": (C.c_int, [C.c_void_p]),
+    "lcu_engine_session_new": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(SampleArgs), C.POINTER(C.c_uint64)]),
+    "lcu_engine_start": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32, C.c_int]),
+    "lcu_engine_remove": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "lcu_engine_session_pos": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint32)]),
+    "lcu_engine_session_set_pos": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32]),
+    "lcu_engine_prepare": (C.c_int, [C.c_void_p, C.POINTER(RoundInfo)]),
+    "lcu_engine_round_tokens": (C.POINTER(C.c_uint32), [C.c_void_p]),
+    "lcu_engine_round_reqs": (C.POINTER(Req), [C.c_void_p]),
+    "lcu_engine_round_fast_map": (C.POINTER(C.c_uint32), [C.c_void_p]),
+    "lcu_engine_round_sample_args": (C.POINTER(SampleArgs), [C.c_void_p]),
+    "lcu_engine_round_output": (C.POINTER(C.c_uint64), [C.c_void_p]),
+    "lcu_engine_round_finished": (C.POINTER(C.c_uint64), [C.c_void_p]),
+    "lcu_engine_round_overflow": (C.POINTER(C.c_uint64), [C.c_void_p]),
+    "lcu_engine_round_positions": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "lcu_engine_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RoundInfo)]),
     "lcu_op_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "lcu_op_fast_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_op_rms_norm": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_int,

@@ -125,10 +125,12 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
     LCU_REQUIRE(y && x && w && n >= 0 && in > 0 && out > 0, "linear: bad arguments");
     LCU_REQUIRE(w_dt == dt || (w_dt == LCU_Q8_0 && dt == LCU_F16), "linear: weight dtype %d with activation dtype %d", w_dt, dt);
     const size_t eb = 2;
+    const bool batched = n > 4 && gemm_skinny_supported(in, w_dt == LCU_Q8_0) && out % 2 == 0;
+    if (batched) gemm_skinny_set_scratch(nullptr, 0, nullptr, 0);  // the stand-alone operator owns no scratch: no K split
     for (int t0 = 0; t0 < n;) {
-        int nt = gemv_max_tokens(in);
+        int nt = batched ? 64 : gemv_max_tokens(in);
         if (nt > n - t0) nt = n - t0;
-        if (nt == 3) nt = 2;
+        if (nt == 3 && !batched) nt = 2;
         GemvArgs a{};
         a.w = w;
         a.w_q8 = w_dt == LCU_Q8_0;
@@ -145,7 +147,7 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
         a.res = residual ? reinterpret_cast<const unsigned char *>(residual) + (size_t)t0 * stride_res * eb : nullptr;
         a.stride_res = stride_res;
         a.early_prefetch = 1;
-        int rc = gemv_launch(a, dt, as_stream(s), false);
+        int rc = batched ? gemm_skinny_launch(a, dt, as_stream(s), false) : gemv_launch(a, dt, as_stream(s), false);
         if (rc) return rc;
         t0 += nt;
     }

@@ -100,6 +100,18 @@ __device__ __forceinline__ uint4 ld_stream_128(const void *p) {
                  : "l"(p));
     return v;
 }
+// 256-bit streaming load (sm_100): 32 bytes per lane, so the 4 lanes of a quad cover one
+// 128-byte line; evict-first in L2 because weights are used once per step.
+struct u32x8 {
+    uint4 lo, hi;
+};
+__device__ __forceinline__ u32x8 ld_stream_256(const void *p) {
+    u32x8 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(p));
+    return v;
+}
 __device__ __forceinline__ uint2 ld_stream_64(const void *p) {
     uint2 v;
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"

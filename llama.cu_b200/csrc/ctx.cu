@@ -96,7 +96,11 @@ struct lcu_ctx {
 
     // arena (one allocation)
     void *arena = nullptr;
-    void *x = nullptr, *q = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr;
+    void *x = nullptr, *q = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr, *hbuf = nullptr;
+    void *sk_ws = nullptr;
+    unsigned *sk_tickets = nullptr;
+    size_t sk_ws_bytes = 0;
+    bool batched_ok = false;  // tensor-core path for rounds of more than 4 tokens
     void *attn_scratch = nullptr, *sample_ws = nullptr;
     size_t sample_ws_bytes = 0;
     lcu_kv_pair *pre_pairs = nullptr;  // copy of the last round's output pairs (token feedback)
@@ -305,8 +309,9 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     size_t sz_mk_part = align256((size_t)4 * c->nh_l * 16 * (d.dh + 2) * 4);
     size_t sz_mk_best = align256((size_t)grid * 4 * 4);
     size_t sz_mk_phases = align256((size_t)(d.n_layers * 5 + 1) * sizeof(MkPhase));
+    const size_t sz_sk_ws = (size_t)16 << 20, sz_sk_tickets = (size_t)16 << 10;
     size_t total = sz_x + 2 * sz_q + sz_act + sz_logits + sz_attn + c->sample_ws_bytes + sz_pairs + 512 + c->desc_cap +
-                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases;
+                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases + sz_x + sz_sk_ws + sz_sk_tickets;
     cudaError_t e = cudaMalloc(&c->arena, total);
     if (e != cudaSuccess) {
         delete c;
@@ -330,7 +335,11 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     c->mk_attn_part = reinterpret_cast<float *>(p); p += sz_mk_part;
     c->mk_best_v = reinterpret_cast<float *>(p); p += sz_mk_best;
     c->mk_best_i = reinterpret_cast<uint32_t *>(p); p += sz_mk_best;
-    c->mk_phases_dev = reinterpret_cast<MkPhase *>(p);
+    c->mk_phases_dev = reinterpret_cast<MkPhase *>(p); p += sz_mk_phases;
+    c->hbuf = p; p += sz_x;
+    c->sk_ws = p; p += sz_sk_ws;
+    c->sk_tickets = reinterpret_cast<unsigned *>(p);
+    c->sk_ws_bytes = sz_sk_ws;
     for (int i = 0; i < lcu_ctx::RING; ++i) {
         e = cudaMallocHost(reinterpret_cast<void **>(&c->desc_host[i]), c->desc_cap);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->desc_event[i], cudaEventDisableTiming);
@@ -354,6 +363,18 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
         if (rc) {
             lcu_ctx_destroy(c);
             return rc;
+        }
+        // the batched (tensor-core) form of the linear layers
+        c->batched_ok = gemm_skinny_supported(d.d, q8) && gemm_skinny_supported(c->qd, q8) && gemm_skinny_supported(c->di_l, q8);
+        if (c->batched_ok) {
+            rc = gemm_skinny_warm(d.d, c->qd + 2 * c->kvd, c->dt);
+            if (!rc) rc = gemm_skinny_warm(c->qd, d.d, c->dt);
+            if (!rc) rc = gemm_skinny_warm(c->di_l, d.d, c->dt);
+            if (!rc) rc = gemm_skinny_warm(d.d, d.vocab & ~1, c->dt);
+            if (rc) {
+                lcu_ctx_destroy(c);
+                return rc;
+            }
         }
         // the persistent whole-step kernel: single GPU, unquantised weights, shapes it can tile
         int R, KC, nkc;
@@ -656,26 +677,61 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     };
 
     const int n_splits = attn_splits(c, r.n_tok);
+    const bool batched = c->batched_ok && r.n_tok > 4;
+    gemm_skinny_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096);
+    const int norm_dt = d.norm_dtype;
+    // One linear layer over `n` rows: token groups of <= 4 through the GEMV (RMSNorm fused as its
+    // prologue), or blocks of <= 64 through the tensor-core kernel (activations normalised before).
+    auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
+                      const void *norm_w) -> int {
+        const void *src = xin;
+        int src_stride = stride_in;
+        if (batched && norm) {
+            int rc2 = op_rms_norm(c->hbuf, d.d, xin, stride_in, norm_w, norm_dt, d.eps, n, d.d, dt, s, pdl);
+            if (rc2) return rc2;
+            ++launches;
+            src = c->hbuf;
+            src_stride = d.d;
+        }
+        for (int t0 = 0; t0 < n;) {
+            int nt;
+            if (batched) nt = n - t0 < 64 ? n - t0 : 64;
+            else {
+                nt = gemv_max_tokens(proto.in);
+                if (nt > n - t0) nt = n - t0;
+                if (nt == 3) nt = 2;
+            }
+            GemvArgs a = proto;
+            a.x = reinterpret_cast<const unsigned char *>(src) + (size_t)t0 * src_stride * eb;
+            a.stride_x = src_stride;
+            a.n_tok = nt;
+            a.y = reinterpret_cast<unsigned char *>(yout) + (size_t)t0 * stride_out * eb;
+            a.stride_y = stride_out;
+            if (a.res) { a.res = a.y; a.stride_res = stride_out; }
+            if (a.pos) { a.pos += t0; a.tok_seq += t0; }
+            if (!batched && norm) { a.prologue = PRO_RMSNORM; a.norm_w = norm_w; a.norm_f32 = norm_dt == LCU_F32; a.eps = d.eps; }
+            else a.prologue = PRO_NONE;
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
+            int rc2 = batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl);
+            if (rc2) return rc2;
+            ++launches;
+            t0 += nt;
+        }
+        return LCU_OK;
+    };
     for (int l = 0; l < d.n_layers; ++l) {
         const LayerWeights &W = c->layers[l];
         // --- RMSNorm + QKV projection + RoPE + KV append
-        for (int t0 = 0; t0 < r.n_tok;) {
-            int nt = gemv_max_tokens(d.d);
-            if (nt > r.n_tok - t0) nt = r.n_tok - t0;
-            if (nt == 3) nt = 2;
+        {
             GemvArgs a{};
             a.w = W.qkv; a.w_q8 = q8; a.w_scales = w_scales(W.qkv, (size_t)c->qd + 2 * c->kvd, d.d);
-            a.x = row(c->x, d.d, t0); a.stride_x = d.d; a.n_tok = nt; a.in = d.d; a.out = c->qd + 2 * c->kvd;
-            a.prologue = PRO_RMSNORM; a.norm_w = W.attn_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
-            a.epilogue = EPI_ROPE_KV; a.y = row(c->q, c->qd, t0); a.stride_y = c->qd;
-            a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.pos = pos + t0; a.sin_t = c->sin_t; a.cos_t = c->cos_t;
-            a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req + t0; a.page_table = page_table;
+            a.in = d.d; a.out = c->qd + 2 * c->kvd;
+            a.epilogue = EPI_ROPE_KV;
+            a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.pos = pos; a.sin_t = c->sin_t; a.cos_t = c->cos_t;
+            a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req; a.page_table = page_table;
             a.pt_stride = c->pt_stride;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            rc = gemv_launch(a, dt, s, pdl);
+            rc = linear(a, r.n_tok, c->x, d.d, c->q, c->qd, true, W.attn_norm);
             if (rc) return rc;
-            ++launches;
-            t0 += nt;
         }
         // --- attention over the paged cache
         {
@@ -690,21 +746,14 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             ++launches;
         }
         // --- output projection + residual (rank 0 adds the residual under TP)
-        for (int t0 = 0; t0 < r.n_tok;) {
-            int nt = gemv_max_tokens(c->qd);
-            if (nt > r.n_tok - t0) nt = r.n_tok - t0;
-            if (nt == 3) nt = 2;
+        {
             GemvArgs a{};
             a.w = W.o; a.w_q8 = q8; a.w_scales = w_scales(W.o, d.d, c->qd);
-            a.x = row(c->att, c->qd, t0); a.stride_x = c->qd; a.n_tok = nt; a.in = c->qd; a.out = d.d;
-            a.prologue = PRO_NONE;
+            a.in = c->qd; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
-            a.y = row(c->x, d.d, t0); a.stride_y = d.d; a.res = a.y; a.stride_res = d.d;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            rc = gemv_launch(a, dt, s, pdl);
+            a.res = c->tp_rank == 0 ? c->x : nullptr;
+            rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr);
             if (rc) return rc;
-            ++launches;
-            t0 += nt;
         }
         if (c->tp_size > 1) {
             rc = lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
@@ -712,37 +761,23 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             ++launches;
         }
         // --- RMSNorm + gate|up projection + SwiGLU
-        for (int t0 = 0; t0 < r.n_tok;) {
-            int nt = gemv_max_tokens(d.d);
-            if (nt > r.n_tok - t0) nt = r.n_tok - t0;
-            if (nt == 3) nt = 2;
+        {
             GemvArgs a{};
             a.w = W.gate_up; a.w_q8 = q8; a.w_scales = w_scales(W.gate_up, (size_t)2 * c->di_l, d.d);
-            a.x = row(c->x, d.d, t0); a.stride_x = d.d; a.n_tok = nt; a.in = d.d; a.out = 2 * c->di_l;
-            a.prologue = PRO_RMSNORM; a.norm_w = W.ffn_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
-            a.epilogue = EPI_SWIGLU; a.di = c->di_l; a.y = row(c->act, c->di_l, t0); a.stride_y = c->di_l;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            rc = gemv_launch(a, dt, s, pdl);
+            a.in = d.d; a.out = 2 * c->di_l;
+            a.epilogue = EPI_SWIGLU; a.di = c->di_l;
+            rc = linear(a, r.n_tok, c->x, d.d, c->act, c->di_l, true, W.ffn_norm);
             if (rc) return rc;
-            ++launches;
-            t0 += nt;
         }
         // --- down projection + residual
-        for (int t0 = 0; t0 < r.n_tok;) {
-            int nt = gemv_max_tokens(c->di_l);
-            if (nt > r.n_tok - t0) nt = r.n_tok - t0;
-            if (nt == 3) nt = 2;
+        {
             GemvArgs a{};
             a.w = W.down; a.w_q8 = q8; a.w_scales = w_scales(W.down, d.d, c->di_l);
-            a.x = row(c->act, c->di_l, t0); a.stride_x = c->di_l; a.n_tok = nt; a.in = c->di_l; a.out = d.d;
-            a.prologue = PRO_NONE;
+            a.in = c->di_l; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
-            a.y = row(c->x, d.d, t0); a.stride_y = d.d; a.res = a.y; a.stride_res = d.d;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            rc = gemv_launch(a, dt, s, pdl);
+            a.res = c->tp_rank == 0 ? c->x : nullptr;
+            rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr);
             if (rc) return rc;
-            ++launches;
-            t0 += nt;
         }
         if (c->tp_size > 1) {
             rc = lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
@@ -753,7 +788,25 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
 
     // --- head on the lead rank only (exec/engine.rs:90,201): gather + RMSNorm + LM head + sampling
     if (c->tp_rank == 0) {
-        for (int r0 = 0; r0 < r.n_req;) {
+        const bool head_batched = c->batched_ok && r.n_req > 4;
+        if (head_batched) {
+            // gather the output rows (Embedding reused as a row gather, exec/output_head.rs:75-77), norm, LM head
+            rc = op_embedding(c->hbuf, c->x, out_idx, r.n_req, (size_t)d.d * 2, s, pdl);
+            if (!rc) rc = op_rms_norm(c->hbuf, d.d, c->hbuf, d.d, c->out_norm, norm_dt, d.eps, r.n_req, d.d, dt, s, pdl);
+            if (rc) return rc;
+            launches += 2;
+            for (int r0 = 0; r0 < r.n_req; r0 += 64) {
+                GemvArgs a{};
+                a.w = c->lm_head; a.w_q8 = 0;
+                a.x = row(c->hbuf, d.d, r0); a.stride_x = d.d; a.n_tok = r.n_req - r0 < 64 ? r.n_req - r0 : 64;
+                a.in = d.d; a.out = d.vocab; a.prologue = PRO_NONE; a.epilogue = EPI_STORE;
+                a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
+                rc = gemm_skinny_launch(a, dt, s, pdl);
+                if (rc) return rc;
+                ++launches;
+            }
+        }
+        for (int r0 = 0; r0 < r.n_req && !head_batched;) {
             int nt = gemv_max_tokens(d.d);
             if (nt > r.n_req - r0) nt = r.n_req - r0;
             if (nt == 3) nt = 2;

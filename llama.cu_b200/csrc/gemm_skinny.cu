@@ -1,0 +1,278 @@
+// Batched `Linear` for 5..64 tokens per pass — batched decode rounds and prefill chunks
+// (llama.cu/src/op/linear.rs:17-120; the reference calls cuBLAS GemmEx with m = out,
+// n = bucketed token count, k = in).  Still HBM-bound (<= 64 flop per weight byte), so the
+// design goal is the GEMV's: stream every weight byte exactly once with many 128-bit loads
+// in flight; tensor cores (mma.sync m16n8k16, f32 accumulate) only keep the arithmetic
+// off the critical path.
+//
+//   - a warp owns 8 row PAIRS (16 weight rows = the M of the MMA; the token block is N);
+//     the MMA's rows g and g+8 are the two rows of pair g (adjacent rows, or gate row p and
+//     up row p + di), so a thread ends up holding both values of a pair for its two tokens
+//     and the RoPE / SwiGLU / residual epilogues need no data exchange;
+//   - weights go global -> registers directly as MMA A-fragments: each lane loads 16
+//     contiguous bytes (one 256-bit load) of row g and of row g+8, so the 4 lanes of a quad read a
+//     whole 128-byte line; the K positions inside a 64-wide block are permuted (lane t supplies
+//     k = 16t..16t+15), which is harmless because the activation B-fragments read from shared
+//     memory use the same permutation;
+//   - a CTA is 8 warps = 128 weight rows sharing one activation chunk (256 K values of every
+//     token, double-buffered in shared memory with cp.async, rows beyond the round zero-filled),
+//     so activations are re-read from L2 once per 128 rows only;
+//   - matrices with few rows are split along K across CTAs (grid.y) to fill the SMs; partial
+//     sums go through scratch memory and the last CTA of a row block to arrive (atomic
+//     ticket) adds them in split order, then runs the fused epilogue of the GEMV
+//     (gemv_epilogue) for each (pair, token).
+#include <cstdlib>
+#include <map>
+#include <mutex>
+
+#include "gemv.cuh"
+
+namespace lcu {
+
+constexpr int SK_THREADS = 256;
+constexpr int SK_KBC = 4;             // 64-wide K blocks per activation chunk
+constexpr int SK_XK = SK_KBC * 64;    // K elements per chunk
+constexpr int SK_BP = 64;             // row pairs per CTA (8 warps x 8 pairs = 128 weight rows)
+
+__device__ __forceinline__ void sk_cp_async_16(void *smem_dst, const void *gsrc, bool valid) {
+    unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gsrc), "r"(sz) : "memory");
+}
+
+template <class T> __device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                            uint32_t b0, uint32_t b1);
+template <> __device__ __forceinline__ void mma16816<__half>(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                             uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float c[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// grid = (row blocks of 64 pairs, K splits).  With more than one K split the partial sums go through
+// `ws` [split][pair][token][2] and the last CTA of a row block to arrive (ticket) adds them in split
+// order and runs the epilogue, so the result does not depend on which CTA finishes last.
+template <class T, int NTL>
+__global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_kernel(const GemvArgs a, int n_pairs, float *ws,
+                                                                    unsigned *tickets) {
+    constexpr int N = 8 * NTL;
+    constexpr int ROWB = SK_XK * 2 + 16;  // bytes per activation row in shared memory (+16: bank skew)
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int ksplit = gridDim.y, ks = blockIdx.y;
+    const int Kper = a.in / ksplit;
+    const int k0 = ks * Kper;
+    const int nch = (Kper + SK_XK - 1) / SK_XK;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+
+    const int pair = blockIdx.x * SK_BP + warp * 8 + g;
+    const bool pv = pair < n_pairs;
+    const size_t ra = swiglu ? (size_t)pair : (size_t)pair * 2;
+    const size_t rb = swiglu ? (size_t)pair + a.di : ra + 1;
+    const unsigned char *wbase = reinterpret_cast<const unsigned char *>(a.w);
+    // inside a 64-wide K block lane t4 owns K values [16*t4, 16*t4 + 16): one 256-bit load per row,
+    // and the 4 lanes of a quad read one full 128-byte line
+    const unsigned char *wa = wbase + (pv ? ra : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
+    const unsigned char *wb = wbase + (pv ? rb : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
+    const T *xg = reinterpret_cast<const T *>(a.x);
+
+    float acc[NTL][4];
+#pragma unroll
+    for (int i = 0; i < NTL; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    auto load_x_chunk = [&](int c, int buf) {
+        unsigned char *dst = smem + (size_t)buf * N * ROWB;
+        constexpr int PIECES = N * (SK_XK / 8);  // 16-byte pieces per chunk
+        for (int i = tid; i < PIECES; i += SK_THREADS) {
+            int n = i / (SK_XK / 8), piece = i - n * (SK_XK / 8);
+            int kk = c * SK_XK + piece * 8;
+            bool valid = n < a.n_tok && kk < Kper;
+            const T *src = valid ? xg + (size_t)n * a.stride_x + k0 + kk : xg;
+            sk_cp_async_16(dst + (size_t)n * ROWB + (size_t)piece * 16, src, valid);
+        }
+    };
+    // weights: a rolling window of SK_KBC 64-wide blocks per row in registers; block kb of the next
+    // chunk is requested as soon as block kb of this chunk has been multiplied
+    u32x8 wra[SK_KBC], wrb[SK_KBC];
+    auto load_w = [&](int c, int kb) {
+        int kk = c * SK_XK + kb * 64;
+        bool v = pv && kk < Kper;
+        u32x8 z;
+        z.lo = z.hi = make_uint4(0, 0, 0, 0);
+        wra[kb] = v ? ld_stream_256(wa + (size_t)kk * 2) : z;
+        wrb[kb] = v ? ld_stream_256(wb + (size_t)kk * 2) : z;
+    };
+#pragma unroll
+    for (int kb = 0; kb < SK_KBC; ++kb) load_w(0, kb);
+    grid_dep_wait();
+    load_x_chunk(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    for (int c = 0; c < nch; ++c) {
+        if (c + 1 < nch) load_x_chunk(c + 1, (c + 1) & 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const unsigned char *xs = smem + (size_t)(c & 1) * N * ROWB + (size_t)t4 * 32;
+#pragma unroll
+        for (int kb = 0; kb < SK_KBC; ++kb) {
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) {
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xs + (size_t)(nt * 8 + g) * ROWB + kb * 128);
+                const uint4 x0 = xp[0], x1 = xp[1];
+                mma16816<T>(acc[nt], wra[kb].lo.x, wrb[kb].lo.x, wra[kb].lo.y, wrb[kb].lo.y, x0.x, x0.y);
+                mma16816<T>(acc[nt], wra[kb].lo.z, wrb[kb].lo.z, wra[kb].lo.w, wrb[kb].lo.w, x0.z, x0.w);
+                mma16816<T>(acc[nt], wra[kb].hi.x, wrb[kb].hi.x, wra[kb].hi.y, wrb[kb].hi.y, x1.x, x1.y);
+                mma16816<T>(acc[nt], wra[kb].hi.z, wrb[kb].hi.z, wra[kb].hi.w, wrb[kb].hi.w, x1.z, x1.w);
+            }
+            if (c + 1 < nch) load_w(c + 1, kb);
+        }
+        __syncthreads();
+    }
+
+    if (ksplit == 1) {
+        // a thread holds both rows of its pair for tokens 2t and 2t+1 of every token tile
+        if (pv) {
+#pragma unroll
+            for (int nt = 0; nt < NTL; ++nt) {
+                int n0 = nt * 8 + 2 * t4;
+                if (n0 < a.n_tok) gemv_epilogue<T>(a, pair, n0, acc[nt][0], acc[nt][2]);
+                if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, acc[nt][1], acc[nt][3]);
+            }
+        }
+        return;
+    }
+    // ---- split K: partials to scratch, the last CTA of the row block adds them in split order
+    if (pv) {
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) {
+            float4 v = make_float4(acc[nt][0], acc[nt][2], acc[nt][1], acc[nt][3]);  // (tok 2t: va, vb), (tok 2t+1: va, vb)
+            *reinterpret_cast<float4 *>(ws + (((size_t)ks * n_pairs + pair) * N + nt * 8 + 2 * t4) * 2) = v;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+        s_last = ticket == (unsigned)ksplit - 1;
+        if (s_last) tickets[blockIdx.x] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (pv) {
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < ksplit; ++j) {
+                float4 v = __ldcg(reinterpret_cast<const float4 *>(ws + (((size_t)j * n_pairs + pair) * N + nt * 8 + 2 * t4) * 2));
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            int n0 = nt * 8 + 2 * t4;
+            if (n0 < a.n_tok) gemv_epilogue<T>(a, pair, n0, sum.x, sum.y);
+            if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, sum.z, sum.w);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+bool gemm_skinny_supported(int in, int w_q8) { return !w_q8 && in >= SK_XK && in % 32 == 0; }
+
+// Scratch for split-K partial sums and the per-row-block tickets, handed over by the context.
+static thread_local float *g_ws = nullptr;
+static thread_local size_t g_ws_bytes = 0;
+static thread_local unsigned *g_tickets = nullptr;
+static thread_local int g_n_tickets = 0;
+
+void gemm_skinny_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets) {
+    g_ws = reinterpret_cast<float *>(ws);
+    g_ws_bytes = ws_bytes;
+    g_tickets = tickets;
+    g_n_tickets = n_tickets;
+}
+
+// K splits across CTAs: the count that fills the SMs best (whole waves), smallest on ties.
+static int sk_choose_ksplit(int in, int n_pairs, int n) {
+    const int row_blocks = (n_pairs + SK_BP - 1) / SK_BP;
+    const int sms = sm_count();
+    int best = 1;
+    double best_eff = -1.0;
+    for (int ks = 1; ks <= 8; ks *= 2) {
+        if (in % (ks * 32) || in / ks < SK_XK) break;
+        if (ks > 1 && (!g_ws || (size_t)ks * n_pairs * n * 2 * 4 > g_ws_bytes || row_blocks > g_n_tickets)) break;
+        int ctas = row_blocks * ks;
+        int waves = (ctas + sms - 1) / sms;
+        double eff = (double)ctas / ((double)waves * sms);
+        if (ks > 1) eff -= 0.03 * (ks > 2 ? 2 : 1);  // partial sums cost traffic: prefer fewer splits when close
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+    }
+    return best;
+}
+
+template <class T, int NTL>
+static int sk_inst(const GemvArgs &a, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
+    auto kernel = gemm_skinny_kernel<T, NTL>;
+    constexpr int N = 8 * NTL;
+    size_t smem = (size_t)2 * N * (SK_XK * 2 + 16);
+    static std::mutex mu;
+    static std::map<int, bool> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done[dev]) {
+            if (smem > 48 * 1024) LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done[dev] = true;
+        }
+    }
+    if (dry) return LCU_OK;
+    int ksplit = sk_choose_ksplit(a.in, n_pairs, N);
+    dim3 grid((n_pairs + SK_BP - 1) / SK_BP, ksplit);
+    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(SK_THREADS), smem, s, pdl, a, n_pairs, g_ws, g_tickets));
+    return LCU_OK;
+}
+
+template <class T>
+static int sk_t(const GemvArgs &a, cudaStream_t s, bool pdl, bool dry) {
+    int n_pairs = a.out / 2;
+    int ntl = a.n_tok <= 16 ? 2 : (a.n_tok <= 32 ? 4 : 8);
+    switch (ntl) {
+    case 2: return sk_inst<T, 2>(a, n_pairs, s, pdl, dry);
+    case 4: return sk_inst<T, 4>(a, n_pairs, s, pdl, dry);
+    default: return sk_inst<T, 8>(a, n_pairs, s, pdl, dry);
+    }
+}
+
+int gemm_skinny_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
+    LCU_REQUIRE(a.n_tok >= 1 && a.n_tok <= 64, "gemm_skinny: n_tok = %d (1..64)", a.n_tok);
+    LCU_REQUIRE(gemm_skinny_supported(a.in, a.w_q8), "gemm_skinny: in = %d unsupported", a.in);
+    LCU_REQUIRE(a.out > 0 && a.out % 2 == 0, "gemm_skinny: out = %d must be even", a.out);
+    LCU_REQUIRE(a.prologue == PRO_NONE && !a.x_rows, "gemm_skinny: takes prepared activations only");
+    LCU_REQUIRE(a.stride_x % 8 == 0, "gemm_skinny: x row stride %d must be a multiple of 8 elements", a.stride_x);
+    if (a.epilogue == EPI_SWIGLU) LCU_REQUIRE(a.out == 2 * a.di, "gemm_skinny: swiglu needs out == 2*di");
+    if (dt == LCU_F16) return sk_t<__half>(a, s, pdl, dry);
+    if (dt == LCU_BF16) return sk_t<__nv_bfloat16>(a, s, pdl, dry);
+    set_error("gemm_skinny: activation dtype %d unsupported", dt);
+    return LCU_ERR_INVALID;
+}
+
+int gemm_skinny_warm(int in, int out, int dt) {
+    if (!gemm_skinny_supported(in, 0)) return LCU_OK;
+    for (int n = 16; n <= 64; n *= 2) {
+        GemvArgs a{};
+        a.in = in; a.out = out; a.n_tok = n; a.stride_x = in; a.epilogue = EPI_STORE;
+        int rc = gemm_skinny_launch(a, dt, nullptr, false, true);
+        if (rc) return rc;
+    }
+    return LCU_OK;
+}
+
+}  // namespace lcu

@@ -114,6 +114,13 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
 int gemv_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
 // Prepares (attributes, occupancy) every variant used for this shape without launching.
 int gemv_warm(int in, int out, bool q8, int dt);
+// Batched form for up to 64 tokens per launch (gemm_skinny.cu): same arguments and epilogues, but the
+// activations must be prepared (no RMSNorm prologue, no row gather).
+bool gemm_skinny_supported(int in, int w_q8);
+int gemm_skinny_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
+int gemm_skinny_warm(int in, int out, int dt);
+// Split-K scratch (f32 partial sums) and zeroed tickets (one per 128-row block) for the calling thread.
+void gemm_skinny_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets);
 // Most tokens one launch can take for this input width (activations live in shared memory).
 int gemv_max_tokens(int in);
 

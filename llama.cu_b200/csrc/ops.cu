@@ -64,10 +64,31 @@ __global__ void rms_norm_kernel(T *__restrict__ y, int sy, const T *__restrict__
     grid_dep_wait();
     const T *xr = x + (size_t)blockIdx.x * sx;
     T *yr = y + (size_t)blockIdx.x * sy;
+    // 128-bit path when the row and both strides allow it; the row stays in registers between passes
+    const bool vec = (d % 8 == 0) && (sx % 8 == 0) && (sy % 8 == 0) && d <= 8 * 4 * (int)blockDim.x &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);
+    uint4 keep[4];
     float acc = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = Act<T>::to_f(xr[i]);
-        acc += v * v;
+    if (vec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int i = threadIdx.x + j * blockDim.x;
+            if (i < d / 8) {
+                keep[j] = reinterpret_cast<const uint4 *>(xr)[i];
+                const uint32_t u[4] = {keep[j].x, keep[j].y, keep[j].z, keep[j].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float2 f = Act<T>::to_f2(u[k]);
+                    acc += f.x * f.x;
+                    acc += f.y * f.y;
+                }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            float v = Act<T>::to_f(xr[i]);
+            acc += v * v;
+        }
     }
     __shared__ float part[32];
     __shared__ float rms_s;
@@ -81,6 +102,32 @@ __global__ void rms_norm_kernel(T *__restrict__ y, int sy, const T *__restrict__
     }
     __syncthreads();
     float rms = rms_s;
+    if (vec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int i = threadIdx.x + j * blockDim.x;
+            if (i < d / 8) {
+                float wf[8];
+                if constexpr (sizeof(Tw) == 4) {
+                    float4 w0 = reinterpret_cast<const float4 *>(w)[2 * i], w1 = reinterpret_cast<const float4 *>(w)[2 * i + 1];
+                    wf[0] = w0.x; wf[1] = w0.y; wf[2] = w0.z; wf[3] = w0.w; wf[4] = w1.x; wf[5] = w1.y; wf[6] = w1.z; wf[7] = w1.w;
+                } else {
+                    uint4 wv = reinterpret_cast<const uint4 *>(w)[i];
+                    float2 a = Act<T>::to_f2(wv.x), b = Act<T>::to_f2(wv.y), c = Act<T>::to_f2(wv.z), e = Act<T>::to_f2(wv.w);
+                    wf[0] = a.x; wf[1] = a.y; wf[2] = b.x; wf[3] = b.y; wf[4] = c.x; wf[5] = c.y; wf[6] = e.x; wf[7] = e.y;
+                }
+                float2 f0 = Act<T>::to_f2(keep[j].x), f1 = Act<T>::to_f2(keep[j].y), f2 = Act<T>::to_f2(keep[j].z),
+                       f3 = Act<T>::to_f2(keep[j].w);
+                uint4 o;
+                o.x = Act<T>::pack(rms * f0.x * wf[0], rms * f0.y * wf[1]);
+                o.y = Act<T>::pack(rms * f1.x * wf[2], rms * f1.y * wf[3]);
+                o.z = Act<T>::pack(rms * f2.x * wf[4], rms * f2.y * wf[5]);
+                o.w = Act<T>::pack(rms * f3.x * wf[6], rms * f3.y * wf[7]);
+                reinterpret_cast<uint4 *>(yr)[i] = o;
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = Act<T>::to_f(xr[i]);
         float ww;

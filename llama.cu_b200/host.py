@@ -1,30 +1,35 @@
-"""Host-side session layer above the C-ABI, named after the reference's public API
-(llama.cu/src/lib.rs: `Service`, `Session`, `SessionId`; exec/engine_manager.rs:
-`EngineManager::prepare` -> `Round`).  It decides what goes into each round and calls
-`lcu_step`; all arithmetic happens in the CUDA library.
+"""Session layer above the C-ABI, named after the reference's public API (llama.cu/src/lib.rs:
+`Service`, `Session`; exec/engine_manager.rs: `EngineManager::prepare` -> `Round`).
+
+The round logic itself is the C++ engine inside liblcu.so (csrc/engine.cpp, `lcu_engine_*`); this
+module only wraps it for Python callers.  All arithmetic happens in the CUDA library.
 """
+import ctypes as C
 from dataclasses import dataclass, field
 
 import numpy as np
 
-from . import KVPair, SampleArgs
+from . import RoundInfo, SampleArgs, check, load_library, stream_ptr
 
 
 @dataclass
 class Session:
-    """== `Session{id, sample_args, cache}` (lib.rs / exec/mod.rs:61-69); `pos` is `cache.pos`."""
+    """== `Session{id, sample_args, cache}` (lib.rs / exec/mod.rs:61-69)."""
     id: int
     seq: int
     sample_args: SampleArgs = field(default_factory=SampleArgs.arg_max)
-    pos: int = 0
+    _svc: object = None
 
+    @property
+    def pos(self):
+        """== `cache.pos`: tokens of this session already in its KV cache."""
+        v = C.c_uint32()
+        check(self._svc.lib.lcu_engine_session_pos(self._svc.e, self.id, C.byref(v)))
+        return v.value
 
-@dataclass
-class _Stub:  # == SessionStub (exec/engine.rs:33-66)
-    session: Session
-    seq_len: int
-    remain_steps: int
-    prompt: object
+    @pos.setter
+    def pos(self, value):
+        check(self._svc.lib.lcu_engine_session_set_pos(self._svc.e, self.id, value))
 
 
 @dataclass
@@ -39,83 +44,103 @@ class Round:  # == Round (exec/engine_manager.rs:22-31)
 
 
 class Service:
-    """Continuous batching over one Context: every live session takes part in every round,
-    a new session contributes its whole prompt, a running one a placeholder token that the
-    device overwrites with its previous sample (exec/engine_manager.rs:72-130)."""
+    """Continuous batching over one Context: every live session takes part in every round, a new
+    session contributes its whole prompt, a running one a placeholder token that the device
+    overwrites with its previous sample (exec/engine_manager.rs:72-130)."""
 
-    def __init__(self, ctx, stream=None):
-        import torch
+    def __init__(self, ctx, stream=None, nctx=None):
+        self.lib = load_library()
         self.ctx = ctx
-        self.stream = stream or torch.cuda.Stream(device=ctx.device)
-        self.sess = {}        # id -> _Stub, iterated in id order like the reference's BTreeMap
-        self.pre_output = {}  # id -> index of its pair in the previous round's output
-        self._next_id = 0
-        self._outs = [torch.zeros(ctx.desc.max_seqs or 64, 2, dtype=torch.int32, device=f"cuda:{ctx.device}")
-                      for _ in range(4)]
+        self.nctx = nctx if nctx is not None else ctx.desc.nctx
+        e = C.c_void_p()
+        check(self.lib.lcu_engine_create(ctx.h if ctx is not None else None, self.nctx, C.byref(e)))
+        self.e = e
+        self.sessions = {}
+        self.stream = stream
+        self._outs = None
         self._round = 0
-        self.nctx = ctx.desc.nctx
+        self._next_fake_seq = 0
+        if ctx is not None:
+            import torch
+            self.stream = stream or torch.cuda.Stream(device=ctx.device)
+            self._outs = [torch.zeros(max(ctx.desc.max_seqs, 1) or 64, 2, dtype=torch.int32, device=f"cuda:{ctx.device}")
+                          for _ in range(4)]
+
+    def __del__(self):
+        try:
+            if self.e:
+                self.lib.lcu_engine_destroy(self.e)
+                self.e = None
+        except Exception:
+            pass
 
     def new_session(self, sample_args=None):
-        s = Session(self._next_id, self.ctx.seq_create(), sample_args or SampleArgs.arg_max())
-        self._next_id += 1
+        if self.ctx is not None:
+            seq = self.ctx.seq_create()
+        else:  # host-only use (planning, tests): sequence handles are just labels
+            seq = self._next_fake_seq
+            self._next_fake_seq += 1
+        sid = C.c_uint64()
+        args = sample_args or SampleArgs.arg_max()
+        check(self.lib.lcu_engine_session_new(self.e, seq, C.byref(args), C.byref(sid)))
+        s = Session(sid.value, seq, args, self)
+        self.sessions[s.id] = s
         return s
 
     def start(self, session, prompt, max_steps):
         """== `Terminal::start` (lib.rs:233-243)."""
-        self.sess[session.id] = _Stub(session, len(prompt), max_steps, np.asarray(prompt, dtype=np.uint32))
+        p = np.ascontiguousarray(prompt, dtype=np.uint32)
+        check(self.lib.lcu_engine_start(self.e, session.id, p.ctypes.data, len(p), max_steps))
 
     def stop(self, session_id):
-        stub = self.sess.pop(session_id, None)
-        self.pre_output.pop(session_id, None)
-        return stub.session if stub else None
+        check(self.lib.lcu_engine_remove(self.e, session_id))
+        return self.sessions.get(session_id)
+
+    def _round_from(self, info):
+        lib, e = self.lib, self.e
+        tokens = [lib.lcu_engine_round_tokens(e)[i] for i in range(info.n_tok)]
+        reqs_p = lib.lcu_engine_round_reqs(e)
+        reqs = [(reqs_p[i].seq, reqs_p[i].pos, reqs_p[i].len) for i in range(info.n_req)]
+        fm_p = lib.lcu_engine_round_fast_map(e)
+        fast_map = [(fm_p[2 * i], fm_p[2 * i + 1]) for i in range(info.n_fast)]
+        sa_p = lib.lcu_engine_round_sample_args(e)
+        sample = [SampleArgs(sa_p[i].temperature, sa_p[i].top_p, sa_p[i].top_k) for i in range(info.n_req)]
+        out_p = lib.lcu_engine_round_output(e)
+        output = [(out_p[i], 1) for i in range(info.n_req)]
+        fin_p = lib.lcu_engine_round_finished(e)
+        finished = [self.sessions[fin_p[i]] for i in range(info.n_finished)]
+        ov_p = lib.lcu_engine_round_overflow(e)
+        overflow = [self.sessions[ov_p[i]] for i in range(info.n_overflow)]
+        return Round(overflow, tokens, reqs, sample, output, fast_map, finished)
 
     def prepare(self):
-        """== `EngineManager::prepare`."""
-        r = Round([], [], [], [], [], [], [])
-        out_idx = 0
-        pre_output, self.pre_output = self.pre_output, {}
-        sess, self.sess = self.sess, {}
-        for sid in sorted(sess):
-            stub = sess[sid]
-            s = stub.session
-            end = s.pos + stub.seq_len
-            if end > self.nctx:
-                r.overflow.append(s)
-                continue
-            pos = s.pos
-            s.pos = end
-            r.sample.append(s.sample_args)
-            r.output.append((sid, 1))
-            r.reqs.append((s.seq, pos, stub.seq_len))
-            if stub.prompt is not None:
-                r.tokens.extend(int(t) for t in stub.prompt)
-                stub.prompt = None
-                stub.seq_len = 1
-            else:
-                r.fast_map.append((pre_output[sid], len(r.tokens)))
-                r.tokens.append(0)
-            stub.remain_steps -= 1
-            if stub.remain_steps == 0:
-                r.finished.append(s)
-            else:
-                self.sess[sid] = stub
-                self.pre_output[sid] = out_idx
-            out_idx += 1
-        return r
+        """== `EngineManager::prepare`: builds the next round without running it."""
+        info = RoundInfo()
+        check(self.lib.lcu_engine_prepare(self.e, C.byref(info)))
+        return self._round_from(info)
+
+    def positions(self, round_):
+        """(`pos()`, `out_idx()`) of the round just prepared (exec/engine.rs:352-371)."""
+        pos = np.zeros(len(round_.tokens), np.uint32)
+        out_idx = np.zeros(len(round_.reqs), np.uint32)
+        check(self.lib.lcu_engine_round_positions(self.e, pos.ctypes.data, out_idx.ctypes.data))
+        return pos, out_idx
 
     def step(self, randoms=None):
-        """One round; returns (Round, device tensor of its KVPairs) without synchronising."""
-        r = self.prepare()
-        if not r.tokens:
-            return r, None
+        """One round (`Worker::lead` loop body): returns (Round, device tensor of its KVPairs)
+        without synchronising; (Round, None) when there was nothing to run."""
         out = self._outs[self._round % len(self._outs)]
+        info = RoundInfo()
+        rnd = None
+        if randoms is not None:
+            rnd = np.ascontiguousarray(randoms, dtype=np.float32)
+        else:
+            rnd = np.random.random(max(len(self.sessions), 1)).astype(np.float32)
+        check(self.lib.lcu_engine_step(self.e, stream_ptr(self.stream), rnd.ctypes.data, out.data_ptr(), C.byref(info)))
+        r = self._round_from(info)
+        if info.n_tok == 0:
+            return r, None
         self._round += 1
-        any_sampling = any(not a.is_argmax() for a in r.sample)
-        if any_sampling and randoms is None:
-            randoms = np.random.random(len(r.reqs)).astype(np.float32)
-        self.ctx.step(r.reqs, np.asarray(r.tokens, dtype=np.uint32), out,
-                      args=r.sample if any_sampling else None, randoms=randoms if any_sampling else None,
-                      fast_map=np.asarray(r.fast_map, dtype=np.uint32) if r.fast_map else None, stream=self.stream)
         return r, out
 
     @staticmethod
