@@ -41,13 +41,16 @@ template <class T, int DH, int G>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     constexpr int ROW = DH + 8;        // padded row (elements): 16 extra bytes break bank conflicts
     constexpr int CH = DH / 8;         // 16-byte chunks per row
-    constexpr int NOUT = (G * DH + ATT_THREADS - 1) / ATT_THREADS;
+    constexpr int NP = DH / 2;         // dimension pairs of a head
+    constexpr int NGRP = ATT_THREADS / NP;           // thread groups in the P·V phase
+    constexpr int HG = (G + NGRP - 1) / NGRP;        // heads per group
     extern __shared__ __align__(16) unsigned char smem[];
     T *Ks = reinterpret_cast<T *>(smem);                 // [2][TILE][ROW]
     T *Vs = Ks + 2 * ATT_TILE * ROW;                     // [2][TILE][ROW]
-    float *qs = reinterpret_cast<float *>(Vs + 2 * ATT_TILE * ROW);  // [G][DH]
-    float *S = qs + G * DH;                              // [G][TILE]
-    float *corr = S + G * ATT_TILE;                      // [G]
+    T *qs = Vs + 2 * ATT_TILE * ROW;                     // [G][DH] in the activation dtype
+    float *S = reinterpret_cast<float *>(qs + G * DH);   // [G][TILE] scores, then probabilities
+    float *Sp = S + G * ATT_TILE;                        // [2][G][TILE] half-row partial dots
+    float *corr = Sp + 2 * G * ATT_TILE;                 // [G]
     float *m_run = corr + G;                             // [G]
     float *l_run = m_run + G;                            // [G]
     __shared__ int is_last;
@@ -68,10 +71,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const int tile1 = min(n_tiles, tile0 + tps);
     const float scale = 1.0f / sqrtf((float)DH);
 
-    // q of the G heads of this KV head, as f32
     {
         const T *qg = reinterpret_cast<const T *>(a.q) + (size_t)t * a.stride_q + (size_t)hkv * G * DH;
-        for (int i = tid; i < G * DH; i += ATT_THREADS) qs[i] = Act<T>::to_f(qg[i]);
+        for (int i = tid; i < G * DH; i += ATT_THREADS) qs[i] = qg[i];
         if (tid < G) {
             m_run[tid] = -INFINITY;
             l_run[tid] = 0.f;
@@ -105,9 +107,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
     };
 
-    float acc[NOUT];
+    // P·V ownership: thread = (dimension pair dp, head group gh)
+    const int dp = tid % NP, gh = tid / NP;
+    float acc[HG][2];
 #pragma unroll
-    for (int i = 0; i < NOUT; ++i) acc[i] = 0.f;
+    for (int i = 0; i < HG; ++i) acc[i][0] = acc[i][1] = 0.f;
+    // score ownership: thread = (position j, half of the head dimension hf)
+    const int sj = tid & (ATT_TILE - 1), hf = tid / ATT_TILE;
 
     if (tile0 < tile1) load_tile(tile0, 0);
     cp_async_commit();
@@ -121,42 +127,40 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         const T *kt = Ks + (size_t)stage * ATT_TILE * ROW;
         const T *vt = Vs + (size_t)stage * ATT_TILE * ROW;
 
-        // scores: one (head, position) per thread and pass
-        for (int idx = tid; idx < G * ATT_TILE; idx += ATT_THREADS) {
-            int g = idx / ATT_TILE, j = idx - g * ATT_TILE;
-            float s = -INFINITY;
-            if (tile * ATT_TILE + j < ctx) {
-                const uint4 *kr = reinterpret_cast<const uint4 *>(kt + j * ROW);
-                const float4 *qr = reinterpret_cast<const float4 *>(qs + g * DH);
-                float d0 = 0.f, d1 = 0.f;
+        // scores: a thread reads half of one K row ONCE and dots it with all G query heads
+        // (q is broadcast from shared memory; mixed-precision FMA, no conversions)
+        {
+            const uint4 *kr = reinterpret_cast<const uint4 *>(kt + sj * ROW) + hf * (CH / 2);
+            float d[G];
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    uint4 kv = kr[c];
-                    float4 q0 = qr[2 * c], q1 = qr[2 * c + 1];
-                    float2 k0 = Act<T>::to_f2(kv.x), k1 = Act<T>::to_f2(kv.y), k2 = Act<T>::to_f2(kv.z),
-                           k3 = Act<T>::to_f2(kv.w);
-                    d0 = fmaf(q0.x, k0.x, d0); d1 = fmaf(q0.y, k0.y, d1);
-                    d0 = fmaf(q0.z, k1.x, d0); d1 = fmaf(q0.w, k1.y, d1);
-                    d0 = fmaf(q1.x, k2.x, d0); d1 = fmaf(q1.y, k2.y, d1);
-                    d0 = fmaf(q1.z, k3.x, d0); d1 = fmaf(q1.w, k3.y, d1);
+            for (int g = 0; g < G; ++g) d[g] = 0.f;
+#pragma unroll
+            for (int c = 0; c < CH / 2; ++c) {
+                const uint4 kv = kr[c];
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const uint4 qv = reinterpret_cast<const uint4 *>(qs + g * DH)[hf * (CH / 2) + c];
+                    d[g] = dot8_mixed<T>(kv, qv, d[g]);
                 }
-                s = (d0 + d1) * scale;
             }
-            S[idx] = s;
+#pragma unroll
+            for (int g = 0; g < G; ++g) Sp[(hf * G + g) * ATT_TILE + sj] = d[g];
         }
         __syncthreads();
 
         // online softmax, one warp per head
         for (int g = warp; g < G; g += ATT_THREADS / 32) {
-            float s0 = S[g * ATT_TILE + lane], s1 = S[g * ATT_TILE + lane + 32];
+            const int p0 = tile * ATT_TILE + lane, p1 = p0 + 32;
+            float s0 = p0 < ctx ? (Sp[g * ATT_TILE + lane] + Sp[(G + g) * ATT_TILE + lane]) * scale : -INFINITY;
+            float s1 = p1 < ctx ? (Sp[g * ATT_TILE + lane + 32] + Sp[(G + g) * ATT_TILE + lane + 32]) * scale : -INFINITY;
             float mt = warp_max(fmaxf(s0, s1));
             float mo = m_run[g];
             float mn = fmaxf(mo, mt);
-            float p0 = s0 == -INFINITY ? 0.f : expf(s0 - mn);
-            float p1 = s1 == -INFINITY ? 0.f : expf(s1 - mn);
-            float sum = warp_sum(p0 + p1);
-            S[g * ATT_TILE + lane] = p0;
-            S[g * ATT_TILE + lane + 32] = p1;
+            float pa = s0 == -INFINITY ? 0.f : expf(s0 - mn);
+            float pb = s1 == -INFINITY ? 0.f : expf(s1 - mn);
+            float sum = warp_sum(pa + pb);
+            S[g * ATT_TILE + lane] = pa;
+            S[g * ATT_TILE + lane + 32] = pb;
             if (lane == 0) {
                 float c = mo == -INFINITY ? 0.f : expf(mo - mn);
                 corr[g] = c;
@@ -166,17 +170,24 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
         __syncthreads();
 
-        // P·V: thread owns output elements (g, d)
+        // P·V: a thread owns two adjacent dimensions of HG heads; V is read as packed pairs
 #pragma unroll
-        for (int i = 0; i < NOUT; ++i) {
-            int o = tid + ATT_THREADS * i;
-            if (o < G * DH) {
-                int g = o / DH, d = o - g * DH;
-                float v = acc[i] * corr[g];
+        for (int i = 0; i < HG; ++i) {
+            const int g = gh * HG + i;
+            if (g < G) {
+                float c = corr[g];
+                float o0 = acc[i][0] * c, o1 = acc[i][1] * c;
                 const float *pr = S + g * ATT_TILE;
+                const T *vcol = vt + 2 * dp;
 #pragma unroll 8
-                for (int j = 0; j < ATT_TILE; ++j) v = fmaf(pr[j], Act<T>::to_f(vt[j * ROW + d]), v);
-                acc[i] = v;
+                for (int j = 0; j < ATT_TILE; ++j) {
+                    float2 v = Act<T>::to_f2(*reinterpret_cast<const uint32_t *>(vcol + j * ROW));
+                    float pj = pr[j];
+                    o0 = fmaf(pj, v.x, o0);
+                    o1 = fmaf(pj, v.y, o1);
+                }
+                acc[i][0] = o0;
+                acc[i][1] = o1;
             }
         }
         __syncthreads();
@@ -186,9 +197,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     T *og = reinterpret_cast<T *>(a.o) + (size_t)t * a.stride_o + (size_t)hkv * G * DH;
     if (a.n_splits == 1) {
 #pragma unroll
-        for (int i = 0; i < NOUT; ++i) {
-            int o = tid + ATT_THREADS * i;
-            if (o < G * DH) og[o] = Act<T>::from_f(acc[i] / l_run[o / DH]);
+        for (int i = 0; i < HG; ++i) {
+            const int g = gh * HG + i;
+            if (g < G) {
+                *reinterpret_cast<uint32_t *>(og + g * DH + 2 * dp) = Act<T>::pack(acc[i][0] / l_run[g], acc[i][1] / l_run[g]);
+            }
         }
         return;
     }
@@ -196,11 +209,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     // leave the unnormalised partial and (max, sum); the last split to arrive merges
     const size_t head0 = (size_t)t * a.nh + (size_t)hkv * G;
 #pragma unroll
-    for (int i = 0; i < NOUT; ++i) {
-        int o = tid + ATT_THREADS * i;
-        if (o < G * DH) {
-            int g = o / DH, d = o - g * DH;
-            a.part_o[((head0 + g) * a.n_splits + sp) * DH + d] = acc[i];
+    for (int i = 0; i < HG; ++i) {
+        const int g = gh * HG + i;
+        if (g < G) {
+            float *dst = a.part_o + ((head0 + g) * a.n_splits + sp) * DH + 2 * dp;
+            dst[0] = acc[i][0];
+            dst[1] = acc[i][1];
         }
     }
     if (tid < G) {
@@ -217,21 +231,22 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     if (!is_last) return;
     __threadfence();
 #pragma unroll
-    for (int i = 0; i < NOUT; ++i) {
-        int o = tid + ATT_THREADS * i;
-        if (o < G * DH) {
-            int g = o / DH, d = o - g * DH;
+    for (int i = 0; i < HG; ++i) {
+        const int g = gh * HG + i;
+        if (g < G) {
             const float *ml = a.part_ml + (head0 + g) * a.n_splits * 2;
             float M = -INFINITY;
             for (int s2 = 0; s2 < a.n_splits; ++s2) M = fmaxf(M, __ldcg(ml + 2 * s2));
-            float L = 0.f, O = 0.f;
+            float L = 0.f, O0 = 0.f, O1 = 0.f;
             for (int s2 = 0; s2 < a.n_splits; ++s2) {
                 float ms = __ldcg(ml + 2 * s2), ls = __ldcg(ml + 2 * s2 + 1);
                 float w = ms == -INFINITY ? 0.f : expf(ms - M);
                 L = fmaf(ls, w, L);
-                O = fmaf(__ldcg(a.part_o + ((head0 + g) * a.n_splits + s2) * DH + d), w, O);
+                float2 o = __ldcg(reinterpret_cast<const float2 *>(a.part_o + ((head0 + g) * a.n_splits + s2) * DH + 2 * dp));
+                O0 = fmaf(o.x, w, O0);
+                O1 = fmaf(o.y, w, O1);
             }
-            og[o] = Act<T>::from_f(O / L);
+            *reinterpret_cast<uint32_t *>(og + g * DH + 2 * dp) = Act<T>::pack(O0 / L, O1 / L);
         }
     }
     if (tid == 0) a.counters[(size_t)t * a.nkvh + hkv] = 0;  // ready for the next launch
@@ -261,7 +276,8 @@ void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok) {
 template <class T, int DH, int G>
 static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = attn_kernel<T, DH, G>;
-    size_t smem = (size_t)4 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)(G * DH + G * ATT_TILE + 3 * G) * sizeof(float);
+    size_t smem = (size_t)4 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)G * DH * sizeof(T) +
+                  (size_t)(3 * G * ATT_TILE + 3 * G) * sizeof(float);
     static std::mutex mu;
     static std::map<int, bool> done;
     int dev = 0;

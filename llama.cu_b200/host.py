@@ -63,7 +63,7 @@ class Service:
         if ctx is not None:
             import torch
             self.stream = stream or torch.cuda.Stream(device=ctx.device)
-            self._outs = [torch.zeros(max(ctx.desc.max_seqs, 1) or 64, 2, dtype=torch.int32, device=f"cuda:{ctx.device}")
+            self._outs = [torch.zeros(ctx.desc.max_seqs or 64, 2, dtype=torch.int32, device=f"cuda:{ctx.device}")
                           for _ in range(4)]
 
     def __del__(self):
