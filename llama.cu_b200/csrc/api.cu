@@ -1,5 +1,6 @@
 // C-ABI wrappers of the stand-alone operators, the sampler entry points that replace
 // librandom_sample.so, the Q8_0 repacker and the tensor-parallel weight slicer.
+#include <cstdlib>
 #include <cstring>
 
 #include "attention.cuh"
@@ -127,6 +128,9 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
     const size_t eb = 2;
     const bool batched = n > 4 && gemm_skinny_supported(in, w_dt == LCU_Q8_0) && out % 2 == 0;
     if (batched) gemm_skinny_set_scratch(nullptr, 0, nullptr, 0);  // the stand-alone operator owns no scratch: no K split
+    static const bool tc_on = !(getenv("LCU_TC") && getenv("LCU_TC")[0] == '0');
+    const bool tc = batched && tc_on && n > 8 && gemm_tc_supported(in, w_dt == LCU_Q8_0);
+    if (tc) gemm_tc_set_scratch(nullptr, 0, nullptr, 0, nullptr);
     for (int t0 = 0; t0 < n;) {
         int nt = batched ? 64 : gemv_max_tokens(in);
         if (nt > n - t0) nt = n - t0;
@@ -147,7 +151,8 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
         a.res = residual ? reinterpret_cast<const unsigned char *>(residual) + (size_t)t0 * stride_res * eb : nullptr;
         a.stride_res = stride_res;
         a.early_prefetch = 1;
-        int rc = batched ? gemm_skinny_launch(a, dt, as_stream(s), false) : gemv_launch(a, dt, as_stream(s), false);
+        int rc = tc ? gemm_tc_launch(a, dt, as_stream(s), false)
+                    : (batched ? gemm_skinny_launch(a, dt, as_stream(s), false) : gemv_launch(a, dt, as_stream(s), false));
         if (rc) return rc;
         t0 += nt;
     }

@@ -1,0 +1,390 @@
+// Batched `Linear` on the 5th-generation tensor cores: tcgen05.mma with TMA-fed shared-memory
+// operands and the accumulator in tensor memory (TMEM) — for 9..64 tokens per pass (batched decode
+// rounds and prefill chunks).  Same operator as llama.cu/src/op/linear.rs:17-120 (the reference
+// calls cuBLAS GemmEx with m = out, n = bucketed token count, k = in).
+//
+// The GEMM is computed "swapped": D[128 weight rows x N tokens] += W_tile[128 x 64] · X[N x 64]^T,
+// so the weight dimension fills the 128-row MMA and the small token block is N (16, 32 or 64).
+//   - warp 0 (one lane): TMA producer — cp.async.bulk.tensor.2d loads of the weight tile (two
+//     64-row boxes) and of the activation tile into a ring of stages, 128-byte swizzle,
+//     completion on mbarriers.  Each weight byte is read once from HBM;
+//   - warp 1 (one lane): MMA issuer — four tcgen05.mma (K = 16 each) per stage, accumulating into
+//     TMEM; tcgen05.commit frees the stage and, after the last one, signals the epilogue;
+//   - warps 2..5: epilogue — tcgen05.ld of the 128 x N f32 accumulator into registers, staging
+//     through shared memory, then the same fused epilogues as the GEMV (gemv_epilogue: store,
+//     residual, RoPE + KV append, SwiGLU).  The two rows of a pair sit in one tile (adjacent rows,
+//     or 64 gate rows followed by their 64 up rows);
+//   - matrices with few rows are split along K across CTAs (grid.y); partial sums go through
+//     scratch memory and the last CTA of a row block to arrive adds them in split order.
+// Every mbarrier wait is bounded by a wall-clock limit: on expiry the kernel records a status bit,
+// skips the remaining work, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <cstdlib>
+#include <map>
+#include <mutex>
+
+#include "gemv.cuh"
+
+namespace lcu {
+
+constexpr int TC_THREADS = 192;
+constexpr int TC_BM = 128;         // weight rows per CTA tile
+constexpr int TC_BK = 64;          // K elements per stage (128 bytes: one swizzle row)
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ unsigned long long tc_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint32_t tc_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool tc_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (tc_mbar_try(bar, parity)) return true;
+    unsigned long long t0 = tc_ns();
+    for (unsigned it = 1;; ++it) {
+        if (tc_mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 0 && (*abort_flag || tc_ns() - t0 > TC_WAIT_NS)) return false;
+    }
+}
+__device__ __forceinline__ void tc_tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// shared-memory operand descriptor: K-major tile, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t r[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+
+struct TcShared {
+    unsigned long long full[8], empty[8], tmem_full;
+    uint32_t tmem_base;
+    int abort_flag;
+    int last;
+};
+
+// grid = (row blocks of 128 rows = 64 pairs, K splits); block = 6 warps (producer, MMA, 4 epilogue)
+template <class T>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               int n_pairs, int N, int n_stages, uint32_t idesc, float *ws, unsigned *tickets, uint32_t *status) {
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes
+    unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    const int stage_bytes = TC_A_BYTES + N * 128;
+    float *stg = reinterpret_cast<float *>(smem + (size_t)n_stages * stage_bytes);  // [128][N + 1]
+    TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)TC_BM * (N + 1) * 4);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ksplit = gridDim.y, ks = blockIdx.y;
+    const int Kper = a.in / ksplit, nkb = Kper / TC_BK, k0 = ks * Kper;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+    const int tm_cols = N < 32 ? 32 : N;
+
+    if (tid == 0) {
+        for (int i = 0; i < n_stages; ++i) {
+            tc_mbar_init(tc_smem(&sh->full[i]), 1);
+            tc_mbar_init(tc_smem(&sh->empty[i]), 1);
+        }
+        tc_mbar_init(tc_smem(&sh->tmem_full), 1);
+        sh->abort_flag = 0;
+        sh->last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM allocation is a warp-wide operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)), "r"(tm_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer
+        const int rb = blockIdx.x;
+        const int row_a = swiglu ? rb * 64 : rb * TC_BM;
+        const int row_b = swiglu ? a.di + rb * 64 : rb * TC_BM + 64;
+        grid_dep_wait();
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int slot = kb % n_stages;
+            const uint32_t parity = (uint32_t)(kb / n_stages) & 1u;
+            if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            const uint32_t bar = tc_smem(&sh->full[slot]);
+            const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+            tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
+            const int kx = k0 + kb * TC_BK;
+            tc_tma_2d(dst, &map_w, kx, row_a, bar);
+            tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, row_b, bar);
+            tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int slot = kb % n_stages;
+            const uint32_t parity = (uint32_t)(kb / n_stages) & 1u;
+            if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TC_A_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)
+                tc_mma_f16(tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_commit(tc_smem(&sh->empty[slot]));  // the stage is free once these MMAs have read it
+        }
+        tc_commit(tc_smem(&sh->tmem_full));         // accumulator complete
+    } else if (warp >= 2) {
+        // ---------------- epilogue warps: TMEM -> registers -> shared staging -> fused epilogue
+        const int et = tid - 64;
+        const int q = warp & 3;                      // a warp may only touch TMEM lanes [32q, 32q + 32)
+        const int row = q * 32 + lane;
+        bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full), 0, &sh->abort_flag);
+        if (!ok) {
+            atomicOr(status, 4u);
+            sh->abort_flag = 1;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            for (int c0 = 0; c0 < N; c0 += 16) {
+                uint32_t r[16];
+                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 16; ++i) stg[row * (N + 1) + c0 + i] = __uint_as_float(r[i]);
+            }
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ok) {
+            const int items = 64 * N;
+            if (ksplit == 1) {
+                for (int idx = et; idx < items; idx += 128) {
+                    int j = idx / N, n = idx - j * N;
+                    int p = blockIdx.x * 64 + j;
+                    if (p >= n_pairs || n >= a.n_tok) continue;
+                    int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
+                    gemv_epilogue<T>(a, p, n, stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
+                }
+            } else {
+                for (int idx = et; idx < items; idx += 128) {
+                    int j = idx / N, n = idx - j * N;
+                    int p = blockIdx.x * 64 + j;
+                    if (p >= n_pairs) continue;
+                    int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
+                    float2 v = make_float2(stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
+                    *reinterpret_cast<float2 *>(ws + (((size_t)ks * n_pairs + p) * N + n) * 2) = v;
+                }
+                __threadfence();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (et == 0) {
+                    unsigned ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+                    sh->last = ticket == (unsigned)ksplit - 1;
+                    if (sh->last) tickets[blockIdx.x] = 0;
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (sh->last) {
+                    __threadfence();
+                    for (int idx = et; idx < items; idx += 128) {
+                        int j = idx / N, n = idx - j * N;
+                        int p = blockIdx.x * 64 + j;
+                        if (p >= n_pairs || n >= a.n_tok) continue;
+                        float va = 0.f, vb = 0.f;
+                        for (int s2 = 0; s2 < ksplit; ++s2) {
+                            float2 v = __ldcg(reinterpret_cast<const float2 *>(ws + (((size_t)s2 * n_pairs + p) * N + n) * 2));
+                            va += v.x;
+                            vb += v.y;
+                        }
+                        gemv_epilogue<T>(a, p, n, va, vb);
+                    }
+                }
+            }
+        }
+    }
+    // ---------------- tail: everyone meets, then the allocating warp returns the TMEM columns
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tm_cols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*TcEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                               const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TcEncodeFn tc_encode_fn() {
+    static TcEncodeFn fn = nullptr;
+    static bool tried = false;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TcEncodeFn>(p);
+    }
+    return fn;
+}
+
+// 2-D map of a row-major [rows, cols] matrix of 16-bit elements; box = 64 columns x box_rows rows, 128-byte swizzle
+static int tc_make_map(CUtensorMap *m, const void *base, int dt, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                       uint32_t box_rows) {
+    TcEncodeFn fn = tc_encode_fn();
+    if (!fn) {
+        set_error("gemm_tc: cuTensorMapEncodeTiled is not available");
+        return LCU_ERR_CUDA;
+    }
+    cuuint64_t gdim[2] = {cols, rows};
+    cuuint64_t gstr[1] = {row_stride * 2};
+    cuuint32_t box[2] = {TC_BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, dt == LCU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void *>(base), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("gemm_tc: cuTensorMapEncodeTiled failed with %d (base %p, %llu x %llu, stride %llu)", (int)r, base,
+                  (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)row_stride);
+        return LCU_ERR_CUDA;
+    }
+    return LCU_OK;
+}
+
+// status word for callers that have no context (the stand-alone operator)
+static __device__ uint32_t g_tc_fallback_status;
+
+static thread_local float *g_tc_ws = nullptr;
+static thread_local size_t g_tc_ws_bytes = 0;
+static thread_local unsigned *g_tc_tickets = nullptr;
+static thread_local int g_tc_n_tickets = 0;
+static thread_local uint32_t *g_tc_status = nullptr;
+
+void gemm_tc_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets, uint32_t *status) {
+    g_tc_ws = reinterpret_cast<float *>(ws);
+    g_tc_ws_bytes = ws_bytes;
+    g_tc_tickets = tickets;
+    g_tc_n_tickets = n_tickets;
+    g_tc_status = status;
+}
+
+bool gemm_tc_supported(int in, int w_q8) { return !w_q8 && in >= TC_BK && in % TC_BK == 0 && tc_encode_fn() != nullptr; }
+
+static size_t tc_smem_bytes(int N, int stages) {
+    return 1024 + (size_t)stages * (TC_A_BYTES + N * 128) + (size_t)TC_BM * (N + 1) * 4 + sizeof(TcShared) + 64;
+}
+
+static int tc_choose_ksplit(int in, int n_pairs, int N) {
+    const int row_blocks = (n_pairs + 63) / 64;
+    const int sms = sm_count();
+    int best = 1;
+    double best_eff = -1.0;
+    for (int ks = 1; ks <= 8; ks *= 2) {
+        if (in % (ks * TC_BK) || in / ks < 4 * TC_BK) break;
+        if (ks > 1 && (!g_tc_ws || (size_t)ks * n_pairs * N * 2 * 4 > g_tc_ws_bytes || row_blocks > g_tc_n_tickets)) break;
+        int ctas = row_blocks * ks;
+        int waves = (ctas + sms - 1) / sms;
+        double eff = (double)ctas / ((double)waves * sms);
+        if (ks > 1) eff -= 0.03 * (ks > 2 ? 2 : 1);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+    }
+    return best;
+}
+
+template <class T>
+static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
+    auto kernel = gemm_tc_kernel<T>;
+    const int N = a.n_tok <= 16 ? 16 : (a.n_tok <= 32 ? 32 : 64);
+    int stages = 8;
+    while (stages > 2 && tc_smem_bytes(N, stages) > (size_t)227 * 1024) --stages;
+    const size_t smem = tc_smem_bytes(N, stages);
+    static std::mutex mu;
+    static std::map<int, uint32_t *> done;  // device -> fallback status word (also marks the attribute as set)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    uint32_t *status = g_tc_status;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = done.find(dev);
+        if (it == done.end()) {
+            LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            void *p = nullptr;
+            LCU_CHECK_CUDA(cudaGetSymbolAddress(&p, g_tc_fallback_status));
+            it = done.emplace(dev, reinterpret_cast<uint32_t *>(p)).first;
+        }
+        if (!status) status = it->second;
+    }
+    if (dry) return LCU_OK;
+    const int n_pairs = a.out / 2;
+    CUtensorMap mw, mx;
+    int rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, 64);
+    if (rc) return rc;
+    // the activation map has exactly n_tok rows: the rest of the N-row box is out of bounds and zero-filled
+    rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
+    if (rc) return rc;
+    const int ksplit = tc_choose_ksplit(a.in, n_pairs, N);
+    const uint32_t fmt = dt == LCU_BF16 ? 1u : 0u;
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    dim3 grid((n_pairs + 63) / 64, ksplit);
+    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, idesc, g_tc_ws,
+                                 g_tc_tickets, status));
+    return LCU_OK;
+}
+
+int gemm_tc_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
+    LCU_REQUIRE(a.n_tok >= 1 && a.n_tok <= 64, "gemm_tc: n_tok = %d (1..64)", a.n_tok);
+    LCU_REQUIRE(dry || gemm_tc_supported(a.in, a.w_q8), "gemm_tc: in = %d unsupported", a.in);
+    LCU_REQUIRE(a.out > 0 && a.out % 2 == 0, "gemm_tc: out = %d must be even", a.out);
+    LCU_REQUIRE(a.prologue == PRO_NONE && !a.x_rows, "gemm_tc: takes prepared activations only");
+    LCU_REQUIRE(a.stride_x % 8 == 0, "gemm_tc: x row stride %d must be a multiple of 8 elements", a.stride_x);
+    LCU_REQUIRE(dry || (((uintptr_t)a.x | (uintptr_t)a.w) % 16) == 0, "gemm_tc: operands must be 16-byte aligned");
+    if (a.epilogue == EPI_SWIGLU) LCU_REQUIRE(a.out == 2 * a.di, "gemm_tc: swiglu needs out == 2*di");
+    if (dt == LCU_F16) return tc_launch_t<__half>(a, dt, s, pdl, dry);
+    if (dt == LCU_BF16) return tc_launch_t<__nv_bfloat16>(a, dt, s, pdl, dry);
+    set_error("gemm_tc: activation dtype %d unsupported", dt);
+    return LCU_ERR_INVALID;
+}
+
+int gemm_tc_warm(int dt) {
+    GemvArgs a{};
+    a.in = 256; a.out = 256; a.n_tok = 16; a.stride_x = 256; a.epilogue = EPI_STORE;
+    return gemm_tc_launch(a, dt, nullptr, false, true);
+}
+
+}  // namespace lcu

@@ -121,6 +121,11 @@ int gemm_skinny_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
 int gemm_skinny_warm(int in, int out, int dt);
 // Split-K scratch (f32 partial sums) and zeroed tickets (one per 128-row block) for the calling thread.
 void gemm_skinny_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets);
+// tcgen05 / TMEM / TMA form of the batched kernel (gemm_tc.cu): same arguments.
+bool gemm_tc_supported(int in, int w_q8);
+int gemm_tc_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
+int gemm_tc_warm(int dt);
+void gemm_tc_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets, uint32_t *status);
 // Most tokens one launch can take for this input width (activations live in shared memory).
 int gemv_max_tokens(int in);
 
