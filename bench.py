@@ -122,6 +122,36 @@ def cpu_reference(cfg, steps, warmup, budget_s=120.0):
             "ms_per_token": per_tok * 1e3}
 
 
+def probe_linear(n_tok, reps=5):
+    """Small stand-alone case of the linear-layer kernels for profiler captures: `lcu_op_linear` on the
+    gate|up shape of the 8B model [28672 x 4096] over 4 distinct weight matrices in turn (940 MB, larger
+    than L2).  n_tok = 1 runs the GEMV, 5..8 the mma.sync kernel, more the tcgen05 kernel."""
+    import ctypes as C
+    import torch
+    import llama_cu_b200 as L
+    lib = L.load_library()
+    k, out = 4096, 28672
+    ws = [torch.randn(out, k, device="cuda", dtype=torch.float16) * 0.02 for _ in range(4)]
+    x = torch.randn(n_tok, k, device="cuda", dtype=torch.float16)
+    y = torch.empty(n_tok, out, device="cuda", dtype=torch.float16)
+    sp = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def run():
+        for w in ws:
+            L.check(lib.lcu_op_linear(y.data_ptr(), out, x.data_ptr(), k, w.data_ptr(), 0, None, 0, n_tok, k, out, 0, sp))
+    run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / (reps * len(ws)) * 1e3
+    print(json.dumps({"probe": "linear", "tokens": n_tok, "shape": [out, k], "us_per_launch": us,
+                      "GBps": out * k * 2 / us / 1e3}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -131,7 +161,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--probe-linear", type=int, default=0, metavar="TOKENS",
+                    help="run only the small linear-layer case used for profiler captures")
     args = ap.parse_args()
+    if args.probe_linear > 0:
+        probe_linear(args.probe_linear)
+        return
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -311,7 +346,9 @@ def main():
             achieved = wbytes / (per_launch_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "kernel": "gemv_kernel, gate|up projection shape [%d x %d], 1 token" % (rows, cols),
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                    "traffic": None, "us_per_launch": per_launch_ms * 1e3,
+                    # dram__bytes_read + dram__bytes_write of one launch from the committed ncu capture of this
+                    # shape (profiles/gemv_kernel_gate_up_shape_ncu_full.md); other shapes were not captured
+                    "traffic": 238.9e6 if (rows, cols, cfg.wdt) == (28672, 4096, 0) else None, "us_per_launch": per_launch_ms * 1e3,
                     "algorithmic_bytes_per_launch": wbytes}
         step_gbs = step_bytes / args.steps / (ms_per_step * 1e-3) / 1e9
 

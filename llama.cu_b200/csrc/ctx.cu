@@ -158,13 +158,29 @@ static DescLayout desc_layout(int n_tok, int n_req, int pt_stride) {
 // How many ways the context of one token is split across CTAs (flash-decoding).  Fixed
 // per (tokens in the round) so that a captured graph stays valid as contexts grow.
 static int attn_splits(const lcu_ctx *c, int n_tok) {
+    static const int per_sm = [] {
+        const char *e = getenv("LCU_ATTN_CTAS_PER_SM");
+        int v = e ? atoi(e) : 2;
+        return v < 1 ? 1 : v;
+    }();
     int ctas = c->nkvh_l * n_tok;
-    int want = (2 * sm_count() + ctas - 1) / ctas;
+    int want = (per_sm * sm_count() + ctas - 1) / ctas;
     int max_tiles = (c->desc.nctx + 63) / 64;
     if (want > max_tiles) want = max_tiles;
     if (want > 32) want = 32;
     if (want < 1) want = 1;
     return want;
+}
+
+// Fewest tokens in a round for which the linear layers run as batched tensor-core kernels instead of
+// the register-blocked GEMV (measured on the 8B shapes: the GEMV wins up to 2 tokens).
+static int batched_min_tokens() {
+    static const int v = [] {
+        const char *e = getenv("LCU_BATCHED_MIN");
+        int x = e ? atoi(e) : 3;
+        return x < 2 ? 2 : x;
+    }();
+    return v;
 }
 
 static size_t weight_elems(const lcu_ctx *c, int kind) {
@@ -371,6 +387,7 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
             if (!rc) rc = gemm_skinny_warm(c->qd, d.d, c->dt);
             if (!rc) rc = gemm_skinny_warm(c->di_l, d.d, c->dt);
             if (!rc) rc = gemm_skinny_warm(d.d, d.vocab & ~1, c->dt);
+            if (!rc && gemm_tc_supported(d.d, q8)) rc = gemm_tc_warm(c->dt);
             if (rc) {
                 lcu_ctx_destroy(c);
                 return rc;
@@ -677,8 +694,10 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     };
 
     const int n_splits = attn_splits(c, r.n_tok);
-    const bool batched = c->batched_ok && r.n_tok > 4;
+    const bool batched = c->batched_ok && r.n_tok >= batched_min_tokens();
     gemm_skinny_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096);
+    gemm_tc_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096, c->dev_status);
+    static const bool tc_on = !(getenv("LCU_TC") && getenv("LCU_TC")[0] == '0');
     const int norm_dt = d.norm_dtype;
     // One linear layer over `n` rows: token groups of <= 4 through the GEMV (RMSNorm fused as its
     // prologue), or blocks of <= 64 through the tensor-core kernel (activations normalised before).
@@ -712,7 +731,9 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (!batched && norm) { a.prologue = PRO_RMSNORM; a.norm_w = norm_w; a.norm_f32 = norm_dt == LCU_F32; a.eps = d.eps; }
             else a.prologue = PRO_NONE;
             a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            int rc2 = batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl);
+            // more than 8 tokens: tcgen05 / TMEM kernel; 5..8: mma.sync kernel; up to 4: GEMV
+            const bool tc = batched && tc_on && nt > 8 && gemm_tc_supported(a.in, a.w_q8);
+            int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl) : (batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl));
             if (rc2) return rc2;
             ++launches;
             t0 += nt;
@@ -788,7 +809,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
 
     // --- head on the lead rank only (exec/engine.rs:90,201): gather + RMSNorm + LM head + sampling
     if (c->tp_rank == 0) {
-        const bool head_batched = c->batched_ok && r.n_req > 4;
+        const bool head_batched = c->batched_ok && r.n_req >= batched_min_tokens();
         if (head_batched) {
             // gather the output rows (Embedding reused as a row gather, exec/output_head.rs:75-77), norm, LM head
             rc = op_embedding(c->hbuf, c->x, out_idx, r.n_req, (size_t)d.d * 2, s, pdl);
@@ -801,7 +822,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
                 a.x = row(c->hbuf, d.d, r0); a.stride_x = d.d; a.n_tok = r.n_req - r0 < 64 ? r.n_req - r0 : 64;
                 a.in = d.d; a.out = d.vocab; a.prologue = PRO_NONE; a.epilogue = EPI_STORE;
                 a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
-                rc = gemm_skinny_launch(a, dt, s, pdl);
+                const bool tc = tc_on && a.n_tok > 8 && gemm_tc_supported(a.in, 0);
+                rc = tc ? gemm_tc_launch(a, dt, s, pdl) : gemm_skinny_launch(a, dt, s, pdl);
                 if (rc) return rc;
                 ++launches;
             }

@@ -84,17 +84,91 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t r[16]) {
 }
 
 struct TcShared {
-    unsigned long long full[8], empty[8], tmem_full;
+    unsigned long long full[8], empty[8], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
     int last;
 };
 
-// grid = (row blocks of 128 rows = 64 pairs, K splits); block = 6 warps (producer, MMA, 4 epilogue)
+// Vector form of the fused epilogues for one token and 8 consecutive outputs.  Everything a thread reads
+// from global memory for its items (residual, rotation table, page number) is fetched by tc_prefetch
+// before tc_finish stores anything: outputs may alias inputs (the residual is updated in place), so the
+// compiler cannot hoist those loads itself, and a chain of dependent round trips per item is what made
+// the scalar form slow.  Every access is 16 bytes.
+//   STORE / RESIDUAL / ROPE_KV: v[0..7] = 8 consecutive rows;  SWIGLU: v = gate, u = up of 8 pairs
+struct TcPre {
+    uint4 res;
+    float4 sn, cs;
+    uint32_t p;
+    int page;
+};
+
+template <class T>
+__device__ __forceinline__ void tc_prefetch(const GemvArgs &a, int n, int first, TcPre &pre) {
+    if (a.epilogue == EPI_RESIDUAL) {
+        pre.res = *reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.res) + (size_t)n * a.stride_res + first);
+    } else if (a.epilogue == EPI_ROPE_KV) {
+        const int sect = first < a.qd ? 0 : (first < a.qd + a.kvd ? 1 : 2);
+        const int rr = first - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
+        const int e = rr % a.dh;
+        pre.p = a.pos[n];
+        if (sect < 2) {
+            const size_t ti = (size_t)pre.p * (a.dh >> 1) + (e >> 1);
+            pre.sn = *reinterpret_cast<const float4 *>(a.sin_t + ti);
+            pre.cs = *reinterpret_cast<const float4 *>(a.cos_t + ti);
+        }
+        if (sect > 0) pre.page = a.page_table[(size_t)a.tok_seq[n] * a.pt_stride + (pre.p >> a.geom.page_shift)];
+    }
+}
+
+template <class T>
+__device__ __forceinline__ void tc_finish(const GemvArgs &a, int n, int first, float v[8], const float u[8], const TcPre &pre) {
+    T *dst = reinterpret_cast<T *>(a.y) + (size_t)n * a.stride_y + first;
+    if (a.epilogue == EPI_SWIGLU) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = swiglu_act(round_act<T>(v[i]), round_act<T>(u[i]));
+    } else if (a.epilogue == EPI_RESIDUAL) {
+        const uint32_t rw[4] = {pre.res.x, pre.res.y, pre.res.z, pre.res.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 rf = Act<T>::to_f2(rw[i]);
+            v[2 * i] += rf.x;
+            v[2 * i + 1] += rf.y;
+        }
+    } else if (a.epilogue == EPI_ROPE_KV) {
+        const int sect = first < a.qd ? 0 : (first < a.qd + a.kvd ? 1 : 2);
+        const int rr = first - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
+        const int head = rr / a.dh, e = rr - head * a.dh;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = round_act<T>(v[i]);  // the projection is materialised before rope
+        if (sect < 2) {
+            const float sn[4] = {pre.sn.x, pre.sn.y, pre.sn.z, pre.sn.w}, cs[4] = {pre.cs.x, pre.cs.y, pre.cs.z, pre.cs.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float xa = v[2 * i], xb = v[2 * i + 1];
+                v[2 * i] = xa * cs[i] - xb * sn[i];
+                v[2 * i + 1] = xa * sn[i] + xb * cs[i];
+            }
+        }
+        if (sect > 0) {
+            const int slot = pre.p & (a.geom.page_tokens - 1);
+            dst = reinterpret_cast<T *>(a.kv_pool) + a.geom.block_off(pre.page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
+        }
+    }
+    uint4 o;
+    o.x = Act<T>::pack(v[0], v[1]); o.y = Act<T>::pack(v[2], v[3]); o.z = Act<T>::pack(v[4], v[5]); o.w = Act<T>::pack(v[6], v[7]);
+    *reinterpret_cast<uint4 *>(dst) = o;
+}
+
+// Persistent: grid = min(tiles, SMs); a tile is (row block of 128 rows = 64 pairs, K split); CTA c takes
+// tiles c, c + grid, ...  The shared-memory ring keeps running across tiles and the accumulator is
+// double-buffered in TMEM, so the epilogue of one tile overlaps the loads and MMAs of the next.
+// block = 6 warps: TMA producer, MMA issuer, 4 epilogue warps.
 template <class T>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               int n_pairs, int N, int n_stages, uint32_t idesc, float *ws, unsigned *tickets, uint32_t *status) {
+               int n_pairs, int N, int n_stages, int ksplit, int vec, uint32_t idesc, float *ws, unsigned *tickets,
+               uint32_t *status) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes
     unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
@@ -103,17 +177,22 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)TC_BM * (N + 1) * 4);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int ksplit = gridDim.y, ks = blockIdx.y;
-    const int Kper = a.in / ksplit, nkb = Kper / TC_BK, k0 = ks * Kper;
+    const int Kper = a.in / ksplit, nkb = Kper / TC_BK;
     const bool swiglu = a.epilogue == EPI_SWIGLU;
-    const int tm_cols = N < 32 ? 32 : N;
+    const int acc_cols = N < 32 ? 32 : N;      // TMEM columns of one accumulator
+    const int tm_cols = 2 * acc_cols;          // two accumulators
+    const int n_rb = (n_pairs + 63) / 64;
+    const int n_tiles = n_rb * ksplit;
 
     if (tid == 0) {
         for (int i = 0; i < n_stages; ++i) {
             tc_mbar_init(tc_smem(&sh->full[i]), 1);
             tc_mbar_init(tc_smem(&sh->empty[i]), 1);
         }
-        tc_mbar_init(tc_smem(&sh->tmem_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(tc_smem(&sh->tmem_full[i]), 1);
+            tc_mbar_init(tc_smem(&sh->tmem_empty[i]), 1);
+        }
         sh->abort_flag = 0;
         sh->last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -129,79 +208,182 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer
-        const int rb = blockIdx.x;
-        const int row_a = swiglu ? rb * 64 : rb * TC_BM;
-        const int row_b = swiglu ? a.di + rb * 64 : rb * TC_BM + 64;
         grid_dep_wait();
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int slot = kb % n_stages;
-            const uint32_t parity = (uint32_t)(kb / n_stages) & 1u;
-            if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
-                atomicOr(status, 4u);
-                sh->abort_flag = 1;
-                break;
+        int it = 0;  // stages issued so far (all tiles)
+        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x) {
+            const int rb = tile / ksplit, ks = tile - rb * ksplit;
+            const int row_a = swiglu ? rb * 64 : rb * TC_BM;
+            const int row_b = swiglu ? a.di + rb * 64 : rb * TC_BM + 64;
+            const int k0 = ks * Kper;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int slot = it % n_stages;
+                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
+                if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
+                    atomicOr(status, 4u);
+                    sh->abort_flag = 1;
+                    break;
+                }
+                const uint32_t bar = tc_smem(&sh->full[slot]);
+                const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+                tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
+                const int kx = k0 + kb * TC_BK;
+                tc_tma_2d(dst, &map_w, kx, row_a, bar);
+                tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, row_b, bar);
+                tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
             }
-            const uint32_t bar = tc_smem(&sh->full[slot]);
-            const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
-            tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
-            const int kx = k0 + kb * TC_BK;
-            tc_tma_2d(dst, &map_w, kx, row_a, bar);
-            tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, row_b, bar);
-            tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int slot = kb % n_stages;
-            const uint32_t parity = (uint32_t)(kb / n_stages) & 1u;
-            if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
+        int it = 0, ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x, ++ti) {
+            const int ab = ti & 1;
+            // the epilogue must have drained this accumulator (two tiles ago)
+            if (!tc_mbar_wait(tc_smem(&sh->tmem_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, &sh->abort_flag)) {
                 atomicOr(status, 4u);
                 sh->abort_flag = 1;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TC_A_BYTES;
+            const uint32_t d_tmem = tmem + (uint32_t)(ab * acc_cols);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int slot = it % n_stages;
+                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
+                if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
+                    atomicOr(status, 4u);
+                    sh->abort_flag = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TC_A_BYTES;
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k)
-                tc_mma_f16(tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            tc_commit(tc_smem(&sh->empty[slot]));  // the stage is free once these MMAs have read it
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    tc_mma_f16(d_tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit(tc_smem(&sh->empty[slot]));  // the stage is free once these MMAs have read it
+            }
+            tc_commit(tc_smem(&sh->tmem_full[ab]));     // accumulator complete
         }
-        tc_commit(tc_smem(&sh->tmem_full));         // accumulator complete
     } else if (warp >= 2) {
         // ---------------- epilogue warps: TMEM -> registers -> shared staging -> fused epilogue
         const int et = tid - 64;
         const int q = warp & 3;                      // a warp may only touch TMEM lanes [32q, 32q + 32)
         const int row = q * 32 + lane;
-        bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full), 0, &sh->abort_flag);
-        if (!ok) {
-            atomicOr(status, 4u);
-            sh->abort_flag = 1;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
-            for (int c0 = 0; c0 < N; c0 += 16) {
-                uint32_t r[16];
-                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; ++i) stg[row * (N + 1) + c0 + i] = __uint_as_float(r[i]);
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+            const int rb = tile / ksplit, ks = tile - rb * ksplit;
+            const int ab = ti & 1;
+            bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[ab]), (uint32_t)(ti >> 1) & 1u, &sh->abort_flag);
+            if (!ok) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
             }
-        }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok) {
+                for (int c0 = 0; c0 < N; c0 += 16) {
+                    uint32_t r[16];
+                    tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * acc_cols + c0), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) stg[row * (N + 1) + c0 + i] = __uint_as_float(r[i]);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (et == 0) {  // the accumulator may be overwritten from here on
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&sh->tmem_empty[ab])) : "memory");
+            }
+            if (!ok) break;
             const int items = 64 * N;
-            if (ksplit == 1) {
+            if (ksplit == 1 && vec) {
+                // (token, 8 outputs) items; residual vectors are fetched first, then everything is stored
+                const int chunks = swiglu ? 8 : 16;
+                TcPre pre[8];
+                int cnt = 0;
+                for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
+                    int c = idx % chunks, n = idx / chunks;
+                    int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                    if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
+                }
+                cnt = 0;
+                for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
+                    int c = idx % chunks, n = idx / chunks;
+                    int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                    if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
+                    float v[8], u[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        v[i] = stg[(8 * c + i) * (N + 1) + n];
+                        u[i] = swiglu ? stg[(64 + 8 * c + i) * (N + 1) + n] : 0.f;
+                    }
+                    tc_finish<T>(a, n, first, v, u, pre[cnt]);
+                }
+            } else if (ksplit == 1) {
                 for (int idx = et; idx < items; idx += 128) {
                     int j = idx / N, n = idx - j * N;
-                    int p = blockIdx.x * 64 + j;
+                    int p = rb * 64 + j;
                     if (p >= n_pairs || n >= a.n_tok) continue;
                     int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
                     gemv_epilogue<T>(a, p, n, stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
                 }
+            } else if (vec) {
+                // split-K, vector form.  Partial tiles go to scratch token-major, 128 floats per (split, row
+                // block, token); the CTA that takes the last ticket sums them in split order and finishes.
+                for (int idx = et; idx < 16 * N; idx += 128) {
+                    int c = idx & 15, n = idx >> 4;
+                    if (n >= a.n_tok) continue;
+                    float4 lo, hi;
+                    lo.x = stg[(8 * c + 0) * (N + 1) + n]; lo.y = stg[(8 * c + 1) * (N + 1) + n];
+                    lo.z = stg[(8 * c + 2) * (N + 1) + n]; lo.w = stg[(8 * c + 3) * (N + 1) + n];
+                    hi.x = stg[(8 * c + 4) * (N + 1) + n]; hi.y = stg[(8 * c + 5) * (N + 1) + n];
+                    hi.z = stg[(8 * c + 6) * (N + 1) + n]; hi.w = stg[(8 * c + 7) * (N + 1) + n];
+                    float *dst = ws + (((size_t)ks * n_rb + rb) * N + n) * TC_BM + 8 * c;
+                    __stcg(reinterpret_cast<float4 *>(dst), lo);
+                    __stcg(reinterpret_cast<float4 *>(dst + 4), hi);
+                }
+                __threadfence();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (et == 0) {
+                    unsigned ticket = atomicAdd(&tickets[rb], 1u);
+                    sh->last = ticket == (unsigned)ksplit - 1;
+                    if (sh->last) tickets[rb] = 0;
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (sh->last) {
+                    __threadfence();
+                    const int chunks = swiglu ? 8 : 16;
+                    TcPre pre[8];
+                    int cnt = 0;
+                    for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
+                        int c = idx % chunks, n = idx / chunks;
+                        int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                        if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
+                    }
+                    cnt = 0;
+                    for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
+                        int c = idx % chunks, n = idx / chunks;
+                        int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                        if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
+                        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+                        for (int s2 = 0; s2 < ksplit; ++s2) {
+                            const float *src = ws + (((size_t)s2 * n_rb + rb) * N + n) * TC_BM + 8 * c;
+                            float4 lo = __ldcg(reinterpret_cast<const float4 *>(src));
+                            float4 hi = __ldcg(reinterpret_cast<const float4 *>(src + 4));
+                            v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+                            v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+                            if (swiglu) {
+                                float4 l2 = __ldcg(reinterpret_cast<const float4 *>(src + 64));
+                                float4 h2 = __ldcg(reinterpret_cast<const float4 *>(src + 68));
+                                u[0] += l2.x; u[1] += l2.y; u[2] += l2.z; u[3] += l2.w;
+                                u[4] += h2.x; u[5] += h2.y; u[6] += h2.z; u[7] += h2.w;
+                            }
+                        }
+                        tc_finish<T>(a, n, first, v, u, pre[cnt]);
+                    }
+                }
             } else {
                 for (int idx = et; idx < items; idx += 128) {
                     int j = idx / N, n = idx - j * N;
-                    int p = blockIdx.x * 64 + j;
+                    int p = rb * 64 + j;
                     if (p >= n_pairs) continue;
                     int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
                     float2 v = make_float2(stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
@@ -210,16 +392,16 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 __threadfence();
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (et == 0) {
-                    unsigned ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+                    unsigned ticket = atomicAdd(&tickets[rb], 1u);
                     sh->last = ticket == (unsigned)ksplit - 1;
-                    if (sh->last) tickets[blockIdx.x] = 0;
+                    if (sh->last) tickets[rb] = 0;
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (sh->last) {
                     __threadfence();
                     for (int idx = et; idx < items; idx += 128) {
                         int j = idx / N, n = idx - j * N;
-                        int p = blockIdx.x * 64 + j;
+                        int p = rb * 64 + j;
                         if (p >= n_pairs || n >= a.n_tok) continue;
                         float va = 0.f, vb = 0.f;
                         for (int s2 = 0; s2 < ksplit; ++s2) {
@@ -231,6 +413,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                     }
                 }
             }
+            asm volatile("bar.sync 2, 128;" ::: "memory");  // staging buffer is reused by the next tile
         }
     }
     // ---------------- tail: everyone meets, then the allocating warp returns the TMEM columns
@@ -310,18 +493,22 @@ static size_t tc_smem_bytes(int N, int stages) {
     return 1024 + (size_t)stages * (TC_A_BYTES + N * 128) + (size_t)TC_BM * (N + 1) * 4 + sizeof(TcShared) + 64;
 }
 
+// K splits: tiles are dealt round-robin to the persistent CTAs, so what matters is that the tile count
+// divides well over the SMs; fewer splits win ties (partial sums cost scratch traffic).
 static int tc_choose_ksplit(int in, int n_pairs, int N) {
     const int row_blocks = (n_pairs + 63) / 64;
     const int sms = sm_count();
     int best = 1;
     double best_eff = -1.0;
-    for (int ks = 1; ks <= 8; ks *= 2) {
-        if (in % (ks * TC_BK) || in / ks < 4 * TC_BK) break;
-        if (ks > 1 && (!g_tc_ws || (size_t)ks * n_pairs * N * 2 * 4 > g_tc_ws_bytes || row_blocks > g_tc_n_tickets)) break;
-        int ctas = row_blocks * ks;
-        int waves = (ctas + sms - 1) / sms;
-        double eff = (double)ctas / ((double)waves * sms);
-        if (ks > 1) eff -= 0.03 * (ks > 2 ? 2 : 1);
+    for (int ks = 1; ks <= 16; ks *= 2) {
+        if (in % (ks * TC_BK) || in / ks < 2 * TC_BK) break;
+        if (ks > 1 && (!g_tc_ws || (size_t)ks * row_blocks * 64 * N * 2 * 4 > g_tc_ws_bytes || row_blocks > g_tc_n_tickets)) break;
+        if (ks > 1 && row_blocks * (ks / 2) >= sms) break;  // split only while the SMs are not all busy
+        int tiles = row_blocks * ks;
+        int rounds = (tiles + sms - 1) / sms;
+        double eff = (double)tiles / ((double)rounds * sms);
+        if (tiles < sms) eff = (double)tiles / sms;
+        eff -= 0.02 * (ks > 1) + 0.01 * (ks > 2) + 0.01 * (ks > 4) + 0.02 * (ks > 8);
         if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
     }
     return best;
@@ -361,9 +548,17 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     const int ksplit = tc_choose_ksplit(a.in, n_pairs, N);
     const uint32_t fmt = dt == LCU_BF16 ? 1u : 0u;
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-    dim3 grid((n_pairs + 63) / 64, ksplit);
-    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, idesc, g_tc_ws,
-                                 g_tc_tickets, status));
+    const int n_tiles = ((n_pairs + 63) / 64) * ksplit;
+    dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
+    // 16-byte epilogue accesses need aligned, 8-divisible outputs
+    bool vec_ok = a.stride_y % 8 == 0 && ((uintptr_t)a.y % 16) == 0 && (a.epilogue == EPI_SWIGLU ? a.di % 8 == 0 : a.out % 8 == 0);
+    if (a.epilogue == EPI_RESIDUAL) vec_ok = vec_ok && a.stride_res % 8 == 0 && ((uintptr_t)a.res % 16) == 0;
+    if (a.epilogue == EPI_ROPE_KV)
+        vec_ok = vec_ok && a.dh % 8 == 0 && a.qd % 8 == 0 && a.kvd % 8 == 0 && ((uintptr_t)a.kv_pool % 16) == 0 &&
+                 ((uintptr_t)a.sin_t % 16) == 0 && ((uintptr_t)a.cos_t % 16) == 0;
+    const int vec = vec_ok ? 1 : 0;
+    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, ksplit, vec, idesc,
+                                 g_tc_ws, g_tc_tickets, status));
     return LCU_OK;
 }
 
