@@ -98,6 +98,11 @@ def cpu_reference(cfg, steps, warmup, budget_s=120.0):
     import numpy as np
     from llama_cu_b200.model import reduced
     from oracle import oracle as O
+    try:
+        host_cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        host_cores = os.cpu_count() or 1
+    cores = O.set_threads(host_cores)  # torchrun exports OMP_NUM_THREADS=1
     layers = min(cfg.n_layers, 4)
     small = reduced(cfg, layers)
     m = O.Model(small, None, act_dtype=2)
@@ -115,7 +120,6 @@ def cpu_reference(cfg, steps, warmup, budget_s=120.0):
         if time.time() - t_start > budget_s and len(times) >= 3:
             break
     per_tok = sum(times) / len(times)
-    cores = os.cpu_count() or 1
     return {"value": 1.0 / per_tok, "unit": "tokens/s", "cores": cores, "kind": "port",
             "sample": f"{layers} of {cfg.n_layers} layers + full LM head in f32, batch 1, 16-token prompt, "
                       f"{len(times)} decode steps; layer time scaled to {cfg.n_layers} layers",

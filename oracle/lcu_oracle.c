@@ -492,6 +492,13 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
     return 0;
 }
 
+/* Worker threads of the parallel loops: launchers such as torchrun export OMP_NUM_THREADS=1, so a
+ * caller that wants every host core asks for them here.  Returns the count now in effect. */
+int orc_set_threads(int n) {
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+}
+
 void orc_last_times(orc_model *m, double *t_layers, double *t_head) {
     *t_layers = m->t_layers;
     *t_head = m->t_head;

@@ -88,6 +88,7 @@ int orc_forward(orc_model *m, int n_req, const int *seqs, const uint32_t *tokens
 int orc_last_hidden(orc_model *m, float *out, size_t cap);
 /* wall-clock seconds the last orc_forward spent in the layers and in the head */
 void orc_last_times(orc_model *m, double *t_layers, double *t_head);
+int orc_set_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -56,6 +56,8 @@ def lib():
         L.orc_seq_free.argtypes = [C.c_void_p, C.c_int]
         L.orc_forward.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 6
         L.orc_last_hidden.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        L.orc_set_threads.argtypes = [C.c_int]
+        L.orc_set_threads.restype = C.c_int
         L.orc_last_times.argtypes = [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_double)]
         L.orc_to_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]
         L.orc_from_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]
@@ -265,3 +267,8 @@ def ref_lib():
         R.sample_half.argtypes = [vp, vp, vp, C.c_size_t, f, f, f, C.c_size_t, vp, C.c_size_t, vp]
         _ref = R
     return _ref
+
+
+def set_threads(n):
+    """Sets the OpenMP thread count of the oracle (0 = leave as is); returns the count in effect."""
+    return int(lib().orc_set_threads(int(n)))
