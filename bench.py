@@ -234,6 +234,14 @@ def main():
                        max_tokens=1024, max_seqs=max(batch, 1), nctx=nctx)
     del weights
     torch.cuda.empty_cache()
+    # tensor parallelism: all-reduce fused into the projections over NVLink peer memory (LCU_BENCH_NCCL=1: ncclAllReduce)
+    if world > 1 and os.environ.get("LCU_BENCH_NCCL", "0") != "1":
+        def gather(b):
+            got = [None] * world
+            dist.all_gather_object(got, b)
+            return got
+        ctx.p2p_connect(gather)
+    config["tp_collectives"] = "peer-memory push + local reduce" if (world > 1 and ctx.p2p_enabled) else ("nccl" if world > 1 else "none")
 
     stream = torch.cuda.Stream(device=dev)
     out = torch.zeros(batch, 2, dtype=torch.int32, device=dev)

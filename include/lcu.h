@@ -293,6 +293,19 @@ LCU_API int lcu_comm_unique_id(void *id128);                                   /
 LCU_API int lcu_comm_init_rank(const void *id128, int rank, int size, void **comm_out);
 LCU_API int lcu_comm_destroy(void *comm);
 
+/* Tensor parallelism over NVLink peer memory instead of NCCL, for the two all-reduces of a layer
+ * (llama.cu/src/op/all_reduce.rs:36-40) and the token broadcast (exec/engine.rs:264-274).  One
+ * process per GPU: every rank calls lcu_p2p_create (allocates its exchange region, returns its
+ * 64-byte CUDA IPC handle), the host gathers the tp_size handles in rank order by any means, every
+ * rank calls lcu_p2p_attach with all of them.  From then on lcu_step lets the output / down
+ * projection kernels store their partials straight into every rank's region and replaces the
+ * collective by a small local reduction.  Waits are bounded: a peer that never arrives raises bit
+ * 16 (all-reduce) or 32 (broadcast) of lcu_device_status instead of hanging.  All ranks must attach
+ * (or none), and all must destroy their contexts only after every rank has finished stepping. */
+LCU_API int lcu_p2p_create(lcu_ctx *ctx, void *handle64_out);
+LCU_API int lcu_p2p_attach(lcu_ctx *ctx, const void *handles /* tp_size x 64 bytes */);
+LCU_API int lcu_p2p_enabled(const lcu_ctx *ctx);
+
 #ifdef __cplusplus
 }
 #endif

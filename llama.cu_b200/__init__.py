@@ -146,6 +146,9 @@ _SIGNATURES = {
     "lcu_comm_unique_id": (C.c_int, [C.c_void_p]),
     "lcu_comm_init_rank": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]),
     "lcu_comm_destroy": (C.c_int, [C.c_void_p]),
+    "lcu_p2p_create": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "lcu_p2p_attach": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "lcu_p2p_enabled": (C.c_int, [C.c_void_p]),
 }
 
 
@@ -338,6 +341,20 @@ class Context:
         out = (C.c_longlong * 16)()
         check(self.lib.lcu_profile_counters(self.h, int(enable), out))
         return list(out)
+
+    def p2p_connect(self, all_gather_bytes):
+        """Switches tensor parallelism from NCCL to NVLink peer memory.  `all_gather_bytes(b)` must return
+        the list of every rank's 64-byte `b` in rank order (e.g. built on `torch.distributed.all_gather_object`);
+        all ranks call this together."""
+        buf = (C.c_ubyte * 64)()
+        check(self.lib.lcu_p2p_create(self.h, buf))
+        handles = all_gather_bytes(bytes(buf))
+        blob = b"".join(handles)
+        check(self.lib.lcu_p2p_attach(self.h, C.c_char_p(blob)))
+
+    @property
+    def p2p_enabled(self):
+        return bool(self.lib.lcu_p2p_enabled(self.h))
 
     def set_megakernel(self, enabled):
         check(self.lib.lcu_set_megakernel(self.h, int(enabled)))

@@ -14,6 +14,7 @@
 #include "gemv.cuh"
 #include "megakernel.cuh"
 #include "ops.cuh"
+#include "p2p.cuh"
 #include "sample.cuh"
 
 namespace lcu {
@@ -128,6 +129,9 @@ struct lcu_ctx {
     long long *mk_prof = nullptr;
     bool mk_profile = false;
 
+    // tensor parallelism over peer memory (set up by lcu_p2p_create / lcu_p2p_attach)
+    P2pState p2p;
+
     bool use_graph = true;
     std::map<std::vector<int>, StepGraph> graphs;
     int last_launches = 0;
@@ -205,6 +209,14 @@ static void drop_graphs(lcu_ctx *c) {
     for (auto &g : c->graphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     c->graphs.clear();
+}
+
+static void p2p_release(lcu_ctx *c) {
+    P2pState &st = c->p2p;
+    for (int r = 0; r < st.n; ++r)
+        if (r != st.rank && st.base[r]) cudaIpcCloseMemHandle(st.base[r]);
+    if (st.own) cudaFree(st.own);
+    st = P2pState();
 }
 
 extern "C" {
@@ -423,6 +435,7 @@ int lcu_ctx_destroy(lcu_ctx *c) {
     }
     if (c->own_pool && c->pool) cudaFree(c->pool);
     if (c->own_tables) cudaFree(c->own_tables);
+    p2p_release(c);
     if (c->arena) cudaFree(c->arena);
     delete c;
     return LCU_OK;
@@ -676,7 +689,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             ++launches;
         }
         if (c->tp_size > 1) {
-            rc = comm_broadcast(c->comm, tokens, (size_t)r.n_tok * 4, 0, s);
+            rc = c->p2p.ready ? p2p_broadcast_launch(c->p2p, tokens, (size_t)r.n_tok * 4, 0, c->dev_status, s)
+                              : comm_broadcast(c->comm, tokens, (size_t)r.n_tok * 4, 0, s);
             if (rc) return rc;
             ++launches;
         }
@@ -701,8 +715,12 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     const int norm_dt = d.norm_dtype;
     // One linear layer over `n` rows: token groups of <= 4 through the GEMV (RMSNorm fused as its
     // prologue), or blocks of <= 64 through the tensor-core kernel (activations normalised before).
+    const bool p2p = c->tp_size > 1 && c->p2p.ready;
+    c->p2p.parity = 0;  // every step holds an even number of all-reduces, so captured graphs agree on it
+    int linear_ctas = 0;  // CTAs of the launches of the last `linear` call
     auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
-                      const void *norm_w) -> int {
+                      const void *norm_w, bool push = false) -> int {
+        linear_ctas = 0;
         const void *src = xin;
         int src_stride = stride_in;
         if (batched && norm) {
@@ -731,14 +749,24 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (!batched && norm) { a.prologue = PRO_RMSNORM; a.norm_w = norm_w; a.norm_f32 = norm_dt == LCU_F32; a.eps = d.eps; }
             else a.prologue = PRO_NONE;
             a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
+            if (push) p2p_make_push(c->p2p, (size_t)t0 * stride_out * eb, &a.push);
             // more than 8 tokens: tcgen05 / TMEM kernel; 5..8: mma.sync kernel; up to 4: GEMV
             const bool tc = batched && tc_on && nt > 8 && gemm_tc_supported(a.in, a.w_q8);
             int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl) : (batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl));
             if (rc2) return rc2;
             ++launches;
+            linear_ctas += g_linear_last_ctas;
             t0 += nt;
         }
         return LCU_OK;
+    };
+    // sum of every rank's partial of the residual stream: fused peer-memory form, or ncclAllReduce
+    auto all_reduce_x = [&]() -> int {
+        if (c->tp_size == 1) return LCU_OK;
+        ++launches;
+        if (p2p)
+            return p2p_reduce_launch(c->p2p, c->x, (size_t)r.n_tok * d.d, dt, (unsigned)(c->tp_size * linear_ctas), c->dev_status, s);
+        return lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
     };
     for (int l = 0; l < d.n_layers; ++l) {
         const LayerWeights &W = c->layers[l];
@@ -773,14 +801,11 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.in = c->qd; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.res = c->tp_rank == 0 ? c->x : nullptr;
-            rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr);
+            rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr, p2p);
             if (rc) return rc;
         }
-        if (c->tp_size > 1) {
-            rc = lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
-            if (rc) return rc;
-            ++launches;
-        }
+        rc = all_reduce_x();
+        if (rc) return rc;
         // --- RMSNorm + gate|up projection + SwiGLU
         {
             GemvArgs a{};
@@ -797,14 +822,11 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.in = c->di_l; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.res = c->tp_rank == 0 ? c->x : nullptr;
-            rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr);
+            rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr, p2p);
             if (rc) return rc;
         }
-        if (c->tp_size > 1) {
-            rc = lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
-            if (rc) return rc;
-            ++launches;
-        }
+        rc = all_reduce_x();
+        if (rc) return rc;
     }
 
     // --- head on the lead rank only (exec/engine.rs:90,201): gather + RMSNorm + LM head + sampling
@@ -909,6 +931,52 @@ int enqueue_round_mk(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStrea
 }
 
 }  // namespace
+
+// ------------------------------------------------------------------ tensor parallelism over peer memory
+
+extern "C" int lcu_p2p_create(lcu_ctx *c, void *handle64_out) {
+    LCU_REQUIRE(c && handle64_out, "p2p_create: null argument");
+    LCU_REQUIRE(c->tp_size > 1 && c->tp_size <= P2P_MAX_RANKS, "p2p_create: tp_size = %d (2..%d)", c->tp_size, P2P_MAX_RANKS);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    LCU_CHECK_CUDA(cudaSetDevice(c->device));
+    drop_graphs(c);
+    p2p_release(c);
+    P2pState &st = c->p2p;
+    st.rank = c->tp_rank;
+    st.n = c->tp_size;
+    st.slot_bytes = ((size_t)c->max_tokens * c->desc.d * 2 + 255) / 256 * 256;
+    const size_t bcast = (size_t)c->max_tokens * 4;
+    st.hdr_bytes = p2p_header_bytes(bcast);
+    const size_t bytes = p2p_region_bytes(st.n, st.slot_bytes, bcast);
+    LCU_CHECK_CUDA(cudaMalloc(&st.own, bytes));
+    LCU_CHECK_CUDA(cudaMemset(st.own, 0, bytes));
+    LCU_CHECK_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t h;
+    LCU_CHECK_CUDA(cudaIpcGetMemHandle(&h, st.own));
+    memcpy(handle64_out, &h, 64);
+    return LCU_OK;
+}
+
+extern "C" int lcu_p2p_attach(lcu_ctx *c, const void *handles) {
+    LCU_REQUIRE(c && handles, "p2p_attach: null argument");
+    P2pState &st = c->p2p;
+    LCU_REQUIRE(st.own && !st.ready, "p2p_attach: call lcu_p2p_create first (once)");
+    LCU_CHECK_CUDA(cudaSetDevice(c->device));
+    for (int r = 0; r < st.n; ++r) {
+        if (r == st.rank) {
+            st.base[r] = st.own;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, reinterpret_cast<const unsigned char *>(handles) + (size_t)r * 64, 64);
+        LCU_CHECK_CUDA(cudaIpcOpenMemHandle(&st.base[r], h, cudaIpcMemLazyEnablePeerAccess));
+    }
+    drop_graphs(c);
+    st.ready = true;
+    return LCU_OK;
+}
+
+extern "C" int lcu_p2p_enabled(const lcu_ctx *c) { return c && c->p2p.ready ? 1 : 0; }
 
 extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_req *reqs, const uint32_t *tokens,
                         const lcu_sample_args *args, const float *randoms, const uint32_t *fast_map, int n_fast,

@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
                 if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, acc[nt][1], acc[nt][3]);
             }
         }
+        p2p_signal(a.push);
         return;
     }
     // ---- split K: partials to scratch, the last CTA of the row block adds them in split order
@@ -165,7 +166,10 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
         if (s_last) tickets[blockIdx.x] = 0;  // ready for the next launch
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        p2p_signal(a.push);
+        return;
+    }
     __threadfence();
     if (pv) {
 #pragma unroll
@@ -180,6 +184,7 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
             if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, sum.z, sum.w);
         }
     }
+    p2p_signal(a.push);
 }
 
 // ------------------------------------------------------------------ host side
@@ -237,6 +242,7 @@ static int sk_inst(const GemvArgs &a, int n_pairs, cudaStream_t s, bool pdl, boo
     int ksplit = sk_choose_ksplit(a.in, n_pairs, N);
     dim3 grid((n_pairs + SK_BP - 1) / SK_BP, ksplit);
     LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(SK_THREADS), smem, s, pdl, a, n_pairs, g_ws, g_tickets));
+    g_linear_last_ctas = (int)(grid.x * grid.y);
     return LCU_OK;
 }
 

@@ -157,6 +157,12 @@ __device__ __forceinline__ void tc_finish(const GemvArgs &a, int n, int first, f
     }
     uint4 o;
     o.x = Act<T>::pack(v[0], v[1]); o.y = Act<T>::pack(v[2], v[3]); o.z = Act<T>::pack(v[4], v[5]); o.w = Act<T>::pack(v[6], v[7]);
+    if (a.push.n && (a.epilogue == EPI_STORE || a.epilogue == EPI_RESIDUAL)) {
+        // tensor parallelism: the partial goes to every rank's all-reduce slot over peer memory
+        for (int k = 0; k < a.push.n; ++k)
+            *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)n * a.stride_y + first) = o;
+        return;
+    }
     *reinterpret_cast<uint4 *>(dst) = o;
 }
 
@@ -418,6 +424,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     }
     // ---------------- tail: everyone meets, then the allocating warp returns the TMEM columns
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    p2p_signal(a.push);  // no-op without tensor parallelism
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -559,6 +566,7 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     const int vec = vec_ok ? 1 : 0;
     LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, ksplit, vec, idesc,
                                  g_tc_ws, g_tc_tickets, status));
+    g_linear_last_ctas = (int)grid.x;
     return LCU_OK;
 }
 

@@ -234,9 +234,12 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
         }
     }
     if (a.pdl_trigger == 1) grid_dep_launch();
+    p2p_signal(a.push);
 }
 
 // ------------------------------------------------------------------ host side
+
+thread_local int g_linear_last_ctas = 0;
 
 static int tune_int(const char *name, int dflt) {
     const char *v = getenv(name);
@@ -322,6 +325,7 @@ static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaS
     if (grid < 1) grid = 1;
     if (dry) return LCU_OK;  // attributes and occupancy are now cached for this configuration
     LCU_CHECK_CUDA(launch_kernel(kernel, dim3(grid), dim3(block), smem, s, pdl, a, pl.KS, pl.RS, n_pairs));
+    g_linear_last_ctas = grid;
     return LCU_OK;
 }
 

@@ -2,6 +2,7 @@
 // with the neighbouring small operators fused in.  Interface only; kernels in gemv.cu.
 #pragma once
 #include "common.cuh"
+#include "p2p.cuh"
 
 namespace lcu {
 
@@ -45,6 +46,8 @@ struct GemvArgs {
     // tuning: 0 = trigger dependents at kernel start, 1 = after the main loop, 2 = never (implicit at exit)
     int pdl_trigger;
     int early_prefetch;  // 1 = first weight loads before griddepcontrol.wait
+    // tensor parallelism: EPI_STORE / EPI_RESIDUAL outputs go to every rank's all-reduce slot instead of y
+    P2pPush push;
 };
 
 #ifdef __CUDACC__
@@ -59,6 +62,12 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
     switch (a.epilogue) {
     case EPI_STORE: {
         size_t r = (size_t)pair * 2;
+        if (a.push.n) {
+            const uint32_t packed = Act<T>::pack(va, vb);
+            for (int k = 0; k < a.push.n; ++k)
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)t * a.stride_y + r) = packed;
+            break;
+        }
         y[(size_t)t * a.stride_y + r] = Act<T>::from_f(va);
         y[(size_t)t * a.stride_y + r + 1] = Act<T>::from_f(vb);
         break;
@@ -69,7 +78,13 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
         uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
         float2 rf = Act<T>::to_f2(rr);
-        *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = Act<T>::pack(va + rf.x, vb + rf.y);
+        const uint32_t packed = Act<T>::pack(va + rf.x, vb + rf.y);
+        if (a.push.n) {
+            for (int k = 0; k < a.push.n; ++k)
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)t * a.stride_y + r) = packed;
+            break;
+        }
+        *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
         break;
     }
     case EPI_ROPE_KV: {
@@ -126,6 +141,9 @@ bool gemm_tc_supported(int in, int w_q8);
 int gemm_tc_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
 int gemm_tc_warm(int dt);
 void gemm_tc_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets, uint32_t *status);
+// CTAs of the calling thread's most recent linear-layer launch (GEMV or batched): the peer all-reduce
+// counts one arrival per producing CTA.
+extern thread_local int g_linear_last_ctas;
 // Most tokens one launch can take for this input width (activations live in shared memory).
 int gemv_max_tokens(int in);
 

@@ -1,0 +1,71 @@
+// All-reduce of the tensor-parallel decode step over NVLink peer memory, fused with the producing
+// linear layer.  Replaces the `AllReduce` node the reference places after the output and the down
+// projection (llama.cu/src/op/all_reduce.rs:1-41, one ncclAllReduce per node).
+//
+// Protocol (one process per GPU, memory shared through CUDA IPC):
+//   * every rank owns a region  [2 parities][n_ranks sources][max_tokens x d]  plus two arrival
+//     counters and two departure tickets;
+//   * the epilogue of the producing kernel stores its partial row block into slot (parity, me) of
+//     EVERY rank's region (plain peer stores), fences, and each of its CTAs adds 1 to every rank's
+//     arrival counter of that parity;
+//   * a small local kernel on each rank waits (bounded) until its counter reaches
+//     n_ranks x producer CTAs, sums the n_ranks slots in rank order in f32, rounds once and writes
+//     the residual stream; the last of its CTAs to leave zeroes the counter.
+// Two parities alternate from one all-reduce to the next.  A rank can only push into parity p again
+// after it has passed its own reduction of parity p^1, which needs every rank's push of p^1, which
+// every rank issues after finishing its reduction of p: so a slot and its counter are never written
+// while they are still being read or reset.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace lcu {
+
+constexpr int P2P_MAX_RANKS = 8;
+
+// What a producing kernel needs: where to store and whom to tell.  n == 0: plain local output.
+struct P2pPush {
+    void *slot[P2P_MAX_RANKS];          // slot (parity, me) in rank r's region, offset like `y`
+    unsigned *arrive[P2P_MAX_RANKS];    // rank r's arrival counter of this parity
+    int n;
+};
+
+#ifdef __CUDACC__
+// Called by every thread of a producing CTA once all its output stores are issued.
+__device__ __forceinline__ void p2p_signal(const P2pPush &p) {
+    if (p.n == 0) return;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < (unsigned)p.n) atomicAdd_system(p.arrive[threadIdx.x], 1u);
+}
+#endif
+
+struct P2pState {
+    int rank = 0, n = 0;
+    void *own = nullptr;                     // this rank's region (cudaMalloc)
+    void *base[P2P_MAX_RANKS] = {nullptr};   // every rank's region as mapped here
+    size_t slot_bytes = 0;                   // max_tokens * d * 2
+    size_t hdr_bytes = 0;                    // counters (first 256 bytes) + broadcast buffer
+    int parity = 0;                          // of the next all-reduce
+    bool ready = false;
+};
+
+// Region layout: words 0..1 arrival counters, 2..3 departure tickets (per parity), 4 broadcast flag;
+// from byte 256 the broadcast buffer (bcast_bytes); from hdr_bytes the slots.
+size_t p2p_header_bytes(size_t bcast_bytes);
+size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes);
+// Fills `push` for the next all-reduce (current parity) with a byte offset into the slot.
+void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push);
+// Enqueues the local reduction: waits for `expected` arrivals, y[i] = sum over ranks of slot r, elems of
+// the 2-byte activation type; then flips the parity.  status: device word that gets bit 16 on a timed-out wait.
+int p2p_reduce_launch(P2pState &st, void *y, size_t elems, int dt, unsigned expected, uint32_t *status, cudaStream_t s);
+
+// Token broadcast from rank `root` (the reference's `share_inputs`, exec/engine.rs:264-274): the root stores
+// `bytes` (a multiple of 4, at most the broadcast buffer) into every other rank's buffer and raises their flag;
+// the others wait (bounded) for the flag, copy the buffer to `data` and lower the flag.  Ranks are kept in step
+// by the all-reduces between two broadcasts, so one buffer is enough.
+int p2p_broadcast_launch(P2pState &st, void *data, size_t bytes, int root, uint32_t *status, cudaStream_t s);
+
+}  // namespace lcu

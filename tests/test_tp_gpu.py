@@ -16,11 +16,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def run_world(world, name, layers, vocab, steps, tmp_path):
-    out = tmp_path / f"tp{world}.json"
+def run_world(world, name, layers, vocab, steps, tmp_path, mode="nccl"):
+    out = tmp_path / f"tp{world}_{mode}.json"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "tp_worker.py"),
-           name, str(layers), str(vocab), str(steps), str(out)]
+           name, str(layers), str(vocab), str(steps), str(out), mode]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
@@ -35,21 +35,23 @@ def test_tp2_matches_tp1_and_oracle(L, O, name, layers, vocab, tmp_path):
     steps = 8
     one = run_world(1, name, layers, vocab, steps, tmp_path)
     two = run_world(2, name, layers, vocab, steps, tmp_path)
+    peer = run_world(2, name, layers, vocab, steps, tmp_path, "p2p")  # all-reduce fused into the projections
+    assert peer["p2p"] and not two["p2p"] and peer["status"] == 0
     cfg = reduced(L.CONFIGS[name], layers, vocab)
     w = L.synth_weights_numpy(cfg, 0)
     rng = np.random.default_rng(1)
-    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in (9, 40)]
+    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in (5, 9, 40)]
     o_ids, o_lgs = O.Model(cfg, w).generate(prompts, steps)
     tol = 8e-2 if cfg.act_dtype == 1 else 2e-2
-    for got in (one, two):
-        for i in range(2):
+    for got in (one, two, peer):
+        for i in range(3):
             for s in range(steps):
                 if got["ids"][i][s] != o_ids[i][s]:
                     lg = np.sort(o_lgs[i][s])
                     assert lg[-1] - lg[-2] <= 2 * tol, (i, s)
                     break
-    if one["ids"] == two["ids"] == o_ids:
-        a, b = np.array(one["logits_last"]), np.array(two["logits_last"])
-        want = np.array([o_lgs[i][steps - 1] for i in range(2)])
-        assert np.abs(a - want).max() <= tol and np.abs(b - want).max() <= tol
+    want = np.array([o_lgs[i][steps - 1] for i in range(3)])
+    for got in (one, two, peer):
+        if got["ids"] == o_ids:
+            assert np.abs(np.array(got["logits_last"]) - want).max() <= tol
     assert two["launches"] > one["launches"]  # the all-reduces are part of the step

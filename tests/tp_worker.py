@@ -1,9 +1,10 @@
 """One rank of the tensor-parallel parity check; run under torchrun by test_tp_gpu.py:
 
-    python -m torch.distributed.run --nproc-per-node N tests/tp_worker.py <config> <layers> <vocab> <steps> <out.json>
+    python -m torch.distributed.run --nproc-per-node N tests/tp_worker.py <config> <layers> <vocab> <steps> <out.json> [p2p]
 
 Every rank loads its slice of the same seeded weights, all ranks run the same rounds, rank 0
-writes the greedy ids and the last round's logits."""
+writes the greedy ids and the last round's logits.  With `p2p` the all-reduces and the token
+broadcast go over NVLink peer memory instead of NCCL."""
 import ctypes as C
 import json
 import os
@@ -21,6 +22,7 @@ from llama_cu_b200.model import reduced  # noqa: E402
 
 def main():
     name, layers, vocab, steps, out_path = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
+    use_p2p = len(sys.argv) > 6 and sys.argv[6] == "p2p"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
@@ -40,8 +42,15 @@ def main():
     cfg = reduced(L.CONFIGS[name], layers, vocab)
     w = L.synth_weights_numpy(cfg, 0)
     rng = np.random.default_rng(1)
-    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in (9, 40)]
+    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in (5, 9, 40)]
     ctx = L.load_model(cfg, w, device=local, tp_rank=rank, tp_size=world, comm=comm)
+    if use_p2p and world > 1:
+        def gather(b):
+            got = [None] * world
+            dist.all_gather_object(got, b)
+            return got
+        ctx.p2p_connect(gather)
+        assert ctx.p2p_enabled
     stream = torch.cuda.Stream(device=dev)
     n = len(prompts)
     out = torch.zeros(n, 2, dtype=torch.int32, device=dev)
@@ -72,7 +81,9 @@ def main():
             for i in range(n):
                 ids[i].append(int(h[i, 0]))
         lg = ctx.logits(n).float().cpu().numpy()
-        json.dump({"ids": ids, "logits_last": lg.tolist(), "launches": ctx.last_launch_count}, open(out_path, "w"))
+        json.dump({"ids": ids, "logits_last": lg.tolist(), "launches": ctx.last_launch_count,
+                   "status": ctx.device_status(), "p2p": ctx.p2p_enabled}, open(out_path, "w"))
+    assert ctx.device_status() == 0, f"rank {rank}: device status {ctx.device_status()}"
     dist.barrier()
     ctx.close()
     L.check(lib.lcu_comm_destroy(comm))
