@@ -165,6 +165,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, metavar="N",
+                    help="cut the model to its first N layers: a small case for profiler captures, not a bench line")
     ap.add_argument("--probe-linear", type=int, default=0, metavar="TOKENS",
                     help="run only the small linear-layer case used for profiler captures")
     args = ap.parse_args()
@@ -180,9 +182,14 @@ def main():
     import llama_cu_b200 as L
     cname, batch, (pmin, pmax) = WORKLOADS[args.workload]
     cfg = L.CONFIGS[cname]
+    if args.layers > 0:
+        from llama_cu_b200.model import reduced
+        cfg = reduced(cfg, min(args.layers, cfg.n_layers))
     dtype_name = {(0, 0): "f16", (1, 1): "bf16", (0, 3): "f16 activations, q8_0 weights"}[(cfg.act_dtype, cfg.wdt)]
     config = {"workload": args.workload, "shape": cname, "batch": batch, "prompt_tokens": [pmin, pmax],
               "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2 (weights streamed once per step)"}
+    if args.layers > 0:
+        config["layers"] = cfg.n_layers  # profiling case only
 
     if args.impl == "reference":
         # the reference's own CPU implementation does not exist (it is CUDA-only and its Rust

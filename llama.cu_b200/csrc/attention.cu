@@ -45,9 +45,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     constexpr int NGRP = ATT_THREADS / NP;           // thread groups in the P·V phase
     constexpr int HG = (G + NGRP - 1) / NGRP;        // heads per group
     extern __shared__ __align__(16) unsigned char smem[];
-    T *Ks = reinterpret_cast<T *>(smem);                 // [2][TILE][ROW]
-    T *Vs = Ks + 2 * ATT_TILE * ROW;                     // [2][TILE][ROW]
-    T *qs = Vs + 2 * ATT_TILE * ROW;                     // [G][DH] in the activation dtype
+    T *Ks = reinterpret_cast<T *>(smem);                 // [TILE][ROW]
+    T *Vs = Ks + ATT_TILE * ROW;                         // [TILE][ROW]
+    T *qs = Vs + ATT_TILE * ROW;                         // [G][DH] in the activation dtype
     float *S = reinterpret_cast<float *>(qs + G * DH);   // [G][TILE] scores, then probabilities
     float *Sp = S + G * ATT_TILE;                        // [2][G][TILE] half-row partial dots
     float *corr = Sp + 2 * G * ATT_TILE;                 // [G]
@@ -66,7 +66,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const int ctx = paged ? (int)a.tok_pos[t] + 1 : a.pos0 + t + 1;
     const int seq = paged ? a.tok_seq[t] : 0;
     const int n_tiles = (ctx + ATT_TILE - 1) / ATT_TILE;
-    const int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    // splits of THIS token: fixed work per CTA, so short and long contexts of one round balance
+    int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
+    if (a.tiles_per_split > tps) tps = a.tiles_per_split;
+    const int my_splits = (n_tiles + tps - 1) / tps;
+    if (sp >= my_splits) return;
     const int tile0 = sp * tps;
     const int tile1 = min(n_tiles, tile0 + tps);
     const float scale = 1.0f / sqrtf((float)DH);
@@ -81,9 +85,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
     }
 
-    auto load_tile = [&](int tile, int stage) {
-        T *kd = Ks + (size_t)stage * ATT_TILE * ROW;
-        T *vd = Vs + (size_t)stage * ATT_TILE * ROW;
+    auto load_tile = [&](int tile) {
+        T *kd = Ks, *vd = Vs;
 #pragma unroll
         for (int i = 0; i < (ATT_TILE * CH) / ATT_THREADS; ++i) {
             int c = tid + ATT_THREADS * i;
@@ -115,17 +118,14 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     // score ownership: thread = (position j, half of the head dimension hf)
     const int sj = tid & (ATT_TILE - 1), hf = tid / ATT_TILE;
 
-    if (tile0 < tile1) load_tile(tile0, 0);
-    cp_async_commit();
-
+    // One tile buffer per CTA: several CTAs share an SM (shared memory allows 5), so the loads of one
+    // overlap the arithmetic of the others.
     for (int tile = tile0; tile < tile1; ++tile) {
-        const int stage = (tile - tile0) & 1;
-        if (tile + 1 < tile1) load_tile(tile + 1, stage ^ 1);
+        load_tile(tile);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<0>();
         __syncthreads();
-        const T *kt = Ks + (size_t)stage * ATT_TILE * ROW;
-        const T *vt = Vs + (size_t)stage * ATT_TILE * ROW;
+        const T *kt = Ks, *vt = Vs;
 
         // scores: a thread reads half of one K row ONCE and dots it with all G query heads
         // (q is broadcast from shared memory; mixed-precision FMA, no conversions)
@@ -192,10 +192,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
         __syncthreads();
     }
-    cp_async_wait<0>();
 
     T *og = reinterpret_cast<T *>(a.o) + (size_t)t * a.stride_o + (size_t)hkv * G * DH;
-    if (a.n_splits == 1) {
+    if (my_splits == 1) {
 #pragma unroll
         for (int i = 0; i < HG; ++i) {
             const int g = gh * HG + i;
@@ -225,7 +224,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     __syncthreads();
     if (tid == 0) {
         unsigned ticket = atomicAdd(&a.counters[(size_t)t * a.nkvh + hkv], 1u);
-        is_last = ticket == (unsigned)a.n_splits - 1;
+        is_last = ticket == (unsigned)my_splits - 1;
     }
     __syncthreads();
     if (!is_last) return;
@@ -236,9 +235,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         if (g < G) {
             const float *ml = a.part_ml + (head0 + g) * a.n_splits * 2;
             float M = -INFINITY;
-            for (int s2 = 0; s2 < a.n_splits; ++s2) M = fmaxf(M, __ldcg(ml + 2 * s2));
+            for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, __ldcg(ml + 2 * s2));
             float L = 0.f, O0 = 0.f, O1 = 0.f;
-            for (int s2 = 0; s2 < a.n_splits; ++s2) {
+            for (int s2 = 0; s2 < my_splits; ++s2) {
                 float ms = __ldcg(ml + 2 * s2), ls = __ldcg(ml + 2 * s2 + 1);
                 float w = ms == -INFINITY ? 0.f : expf(ms - M);
                 L = fmaf(ls, w, L);
@@ -276,7 +275,7 @@ void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok) {
 template <class T, int DH, int G>
 static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = attn_kernel<T, DH, G>;
-    size_t smem = (size_t)4 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)G * DH * sizeof(T) +
+    size_t smem = (size_t)2 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)G * DH * sizeof(T) +
                   (size_t)(3 * G * ATT_TILE + 3 * G) * sizeof(float);
     static std::mutex mu;
     static std::map<int, bool> done;

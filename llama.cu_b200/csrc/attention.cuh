@@ -23,7 +23,9 @@ struct AttnArgs {
     int stk, shk, stv, shv;  // token / head strides of the caches (elements)
     int pos0;
     // split-KV scratch: partial outputs, (max, sum) pairs and arrival counters
-    int n_splits;
+    int n_splits;          // grid depth = most splits any token of the round can need
+    int tiles_per_split;   // 64-position tiles one CTA walks (0: context / n_splits); a token with a short
+                           // context uses fewer splits and the CTAs beyond them exit at once
     float *part_o;        // [n_tok, nh, n_splits, dh]
     float *part_ml;       // [n_tok, nh, n_splits, 2]
     unsigned *counters;   // [n_tok, nkvh], zero before the first launch; the kernel re-zeroes them

@@ -159,21 +159,40 @@ static DescLayout desc_layout(int n_tok, int n_req, int pt_stride) {
     return L;
 }
 
-// How many ways the context of one token is split across CTAs (flash-decoding).  Fixed
-// per (tokens in the round) so that a captured graph stays valid as contexts grow.
-static int attn_splits(const lcu_ctx *c, int n_tok) {
-    static const int per_sm = [] {
-        const char *e = getenv("LCU_ATTN_CTAS_PER_SM");
-        int v = e ? atoi(e) : 2;
-        return v < 1 ? 1 : v;
+// Split-KV plan of the attention launch for a round of n_tok tokens (flash-decoding): every CTA walks
+// `tps` 64-position tiles, the grid is deep enough for the longest context the cache allows, and a token
+// with a shorter context simply uses fewer of its CTAs.  Fixed per round shape so that a captured graph
+// stays valid as contexts grow.  Rounds with enough tokens to fill the GPU on their own (prefill) are
+// not split.
+static void attn_plan(const lcu_ctx *c, int n_tok, int *n_splits, int *tps) {
+    static const int env_tps = [] {
+        const char *e = getenv("LCU_ATTN_TPS");
+        return e ? atoi(e) : 0;
     }();
-    int ctas = c->nkvh_l * n_tok;
-    int want = (per_sm * sm_count() + ctas - 1) / ctas;
-    int max_tiles = (c->desc.nctx + 63) / 64;
-    if (want > max_tiles) want = max_tiles;
-    if (want > 32) want = 32;
-    if (want < 1) want = 1;
-    return want;
+    const int ctas = c->nkvh_l * n_tok;
+    const int max_tiles = (c->desc.nctx + 63) / 64;
+    if (ctas >= 8 * sm_count() || max_tiles <= 1) {
+        *n_splits = 1;
+        *tps = max_tiles;
+        return;
+    }
+    int t = env_tps > 0 ? env_tps : (ctas * 2 >= sm_count() ? 2 : 1);
+    int z = (max_tiles + t - 1) / t;
+    int z_cap = 2048 / n_tok;  // bounds the partial-output scratch
+    if (z_cap > 64) z_cap = 64;
+    if (z_cap < 1) z_cap = 1;
+    if (z > z_cap) {
+        z = z_cap;
+        t = (max_tiles + z - 1) / z;
+    }
+    *n_splits = z;
+    *tps = t;
+}
+
+static int attn_splits(const lcu_ctx *c, int n_tok) {
+    int z, t;
+    attn_plan(c, n_tok, &z, &t);
+    return z;
 }
 
 // Fewest tokens in a round for which the linear layers run as batched tensor-core kernels instead of
@@ -707,7 +726,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
         return reinterpret_cast<unsigned char *>(base) + (size_t)t * stride_elems * eb;
     };
 
-    const int n_splits = attn_splits(c, r.n_tok);
+    int n_splits, attn_tps;
+    attn_plan(c, r.n_tok, &n_splits, &attn_tps);
     const bool batched = c->batched_ok && r.n_tok >= batched_min_tokens();
     gemm_skinny_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096);
     gemm_tc_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096, c->dev_status);
@@ -788,7 +808,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.q = c->q; a.stride_q = c->qd; a.o = c->att; a.stride_o = c->qd;
             a.n_tok = r.n_tok; a.nh = c->nh_l; a.nkvh = c->nkvh_l; a.dh = d.dh;
             a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req; a.tok_pos = pos;
-            a.page_table = page_table; a.pt_stride = c->pt_stride; a.n_splits = n_splits;
+            a.page_table = page_table; a.pt_stride = c->pt_stride; a.n_splits = n_splits; a.tiles_per_split = attn_tps;
             if (n_splits > 1) attn_bind_scratch(a, c->attn_scratch, c->max_tokens);
             rc = attn_launch(a, dt, s, pdl);
             if (rc) return rc;
