@@ -37,25 +37,43 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t r[4], const void *smem_row) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t r[4], const void *smem_row) {
+    unsigned a = (unsigned)__cvta_generic_to_shared(smem_row);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+// Both products run on tensor cores (mma.sync m16n8k16, f32 accumulation):
+//   scores  S[pos][head] = K[pos][:] . q[head][:]   M = 16 positions per warp, N = 8 head slots (G used), K = dh
+//   output  O[head][d]   = P[head][:] . V[:][d]     M = 16 head slots (G used), N = dh / 4 per warp, K = 64 positions
+// K and V fragments come from the shared-memory tile with ldmatrix (V transposed on the way), the query
+// fragments stay in registers for the whole kernel, probabilities are rounded to the activation dtype
+// before the second product and the row sum is taken over the rounded values.
 template <class T, int DH, int G>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
-    constexpr int ROW = DH + 8;        // padded row (elements): 16 extra bytes break bank conflicts
+    constexpr int ROW = DH + 8;        // padded K/V row (elements): 16 extra bytes keep ldmatrix conflict-free
+    constexpr int PROW = ATT_TILE + 8; // padded probability row
     constexpr int CH = DH / 8;         // 16-byte chunks per row
-    constexpr int NP = DH / 2;         // dimension pairs of a head
-    constexpr int NGRP = ATT_THREADS / NP;           // thread groups in the P·V phase
-    constexpr int HG = (G + NGRP - 1) / NGRP;        // heads per group
+    constexpr int KSTEPS = DH / 16;    // k-steps of the score product
+    constexpr int DW = DH / 4;         // output dimensions per warp
+    constexpr int NT = DW / 8;         // 8-wide output tiles per warp
     extern __shared__ __align__(16) unsigned char smem[];
     T *Ks = reinterpret_cast<T *>(smem);                 // [TILE][ROW]
     T *Vs = Ks + ATT_TILE * ROW;                         // [TILE][ROW]
-    T *qs = Vs + ATT_TILE * ROW;                         // [G][DH] in the activation dtype
-    float *S = reinterpret_cast<float *>(qs + G * DH);   // [G][TILE] scores, then probabilities
-    float *Sp = S + G * ATT_TILE;                        // [2][G][TILE] half-row partial dots
-    float *corr = Sp + 2 * G * ATT_TILE;                 // [G]
+    T *Ps = Vs + ATT_TILE * ROW;                         // [16][PROW] probabilities, rows >= G stay zero
+    float *S = reinterpret_cast<float *>(Ps + 16 * PROW);  // [G][TILE] raw scores
+    float *corr = S + G * ATT_TILE;                      // [G]
     float *m_run = corr + G;                             // [G]
     float *l_run = m_run + G;                            // [G]
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, t4 = lane & 3;
     const int hkv = blockIdx.x, t = blockIdx.y, sp = blockIdx.z;
     const T *kv_pool = reinterpret_cast<const T *>(a.kv_pool);
     const bool paged = kv_pool != nullptr;
@@ -75,9 +93,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const int tile1 = min(n_tiles, tile0 + tps);
     const float scale = 1.0f / sqrtf((float)DH);
 
+    // query fragments (B operand of the score product): head slot gid, k = 16 ks + 2 t4 (+8)
+    uint32_t qb[KSTEPS][2];
     {
-        const T *qg = reinterpret_cast<const T *>(a.q) + (size_t)t * a.stride_q + (size_t)hkv * G * DH;
-        for (int i = tid; i < G * DH; i += ATT_THREADS) qs[i] = qg[i];
+        const T *qg = reinterpret_cast<const T *>(a.q) + (size_t)t * a.stride_q + (size_t)hkv * G * DH + (size_t)gid * DH;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qb[ks][0] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 2 * t4) : 0u;
+            qb[ks][1] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 8 + 2 * t4) : 0u;
+        }
+        for (int i = tid; i < 16 * PROW / 2; i += ATT_THREADS) reinterpret_cast<uint32_t *>(Ps)[i] = 0u;
         if (tid < G) {
             m_run[tid] = -INFINITY;
             l_run[tid] = 0.f;
@@ -85,82 +110,107 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
     }
 
-    auto load_tile = [&](int tile) {
-        T *kd = Ks, *vd = Vs;
-#pragma unroll
-        for (int i = 0; i < (ATT_TILE * CH) / ATT_THREADS; ++i) {
-            int c = tid + ATT_THREADS * i;
-            int j = c / CH, col = c - j * CH;
-            int pos = tile * ATT_TILE + j;
-            bool valid = pos < ctx;
-            const T *ksrc, *vsrc;
-            if (paged) {
-                int page = valid ? a.page_table[(size_t)seq * a.pt_stride + (pos >> a.geom.page_shift)] : 0;
-                int slot = pos & (a.geom.page_tokens - 1);
-                size_t off = a.geom.block_off(page, a.layer, 0, hkv) + (size_t)slot * DH + col * 8;
-                ksrc = kv_pool + (valid ? off : 0);
-                vsrc = kv_pool + (valid ? off + (size_t)a.geom.nkvh * a.geom.page_tokens * DH : 0);
-            } else {
-                const T *kl = reinterpret_cast<const T *>(a.k_lin), *vl = reinterpret_cast<const T *>(a.v_lin);
-                ksrc = valid ? kl + (size_t)pos * a.stk + (size_t)hkv * a.shk + col * 8 : kl;
-                vsrc = valid ? vl + (size_t)pos * a.stv + (size_t)hkv * a.shv + col * 8 : vl;
-            }
-            cp_async_16(kd + j * ROW + col * 8, ksrc, valid);
-            cp_async_16(vd + j * ROW + col * 8, vsrc, valid);
+    // Page numbers are fetched into shared memory a window of tiles at a time (128 pages: 32 to 128 tiles),
+    // so the gathers below have no dependent global load in front of their copies.
+    __shared__ int pg[128];
+    const int ppt = paged ? (ATT_TILE >> a.geom.page_shift > 1 ? ATT_TILE >> a.geom.page_shift : 1) : 1;  // pages per tile
+    const int WT = 128 / ppt;                                                                          // tiles per window
+    auto fetch_window = [&](int tile_first) {
+        if (!paged) return;
+        for (int i = tid; i < 128; i += ATT_THREADS) {
+            const long long first = (long long)tile_first * ATT_TILE + (long long)i * a.geom.page_tokens;
+            pg[i] = first < ctx ? a.page_table[(size_t)seq * a.pt_stride + (int)(first >> a.geom.page_shift)] : 0;
         }
     };
+    const size_t blk = paged ? (size_t)a.geom.page_tokens * DH : 0;
+    const size_t kbase = paged ? ((size_t)(a.layer * 2) * a.geom.nkvh + hkv) * blk : 0;
+    const size_t voff = paged ? (size_t)a.geom.nkvh * blk : 0;
+    const int lcol8 = (tid % CH) * 8, j0 = tid / CH;  // this thread's 16-byte column and first row of a tile
 
-    // P·V ownership: thread = (dimension pair dp, head group gh)
-    const int dp = tid % NP, gh = tid / NP;
-    float acc[HG][2];
+    // gathers the K (which = 0) or V (which = 1) rows of a tile; rows past the context are zero-filled
+    auto load_rows = [&](int tile, int which) {
+        T *dst = which ? Vs : Ks;
+        const int w0 = ((tile - tile0) % WT) * ppt;
 #pragma unroll
-    for (int i = 0; i < HG; ++i) acc[i][0] = acc[i][1] = 0.f;
-    // score ownership: thread = (position j, half of the head dimension hf)
-    const int sj = tid & (ATT_TILE - 1), hf = tid / ATT_TILE;
-
-    // One tile buffer per CTA: several CTAs share an SM (shared memory allows 5), so the loads of one
-    // overlap the arithmetic of the others.
-    for (int tile = tile0; tile < tile1; ++tile) {
-        load_tile(tile);
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-        const T *kt = Ks, *vt = Vs;
-
-        // scores: a thread reads half of one K row ONCE and dots it with all G query heads
-        // (q is broadcast from shared memory; mixed-precision FMA, no conversions)
-        {
-            const uint4 *kr = reinterpret_cast<const uint4 *>(kt + sj * ROW) + hf * (CH / 2);
-            float d[G];
-#pragma unroll
-            for (int g = 0; g < G; ++g) d[g] = 0.f;
-#pragma unroll
-            for (int c = 0; c < CH / 2; ++c) {
-                const uint4 kv = kr[c];
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    const uint4 qv = reinterpret_cast<const uint4 *>(qs + g * DH)[hf * (CH / 2) + c];
-                    d[g] = dot8_mixed<T>(kv, qv, d[g]);
-                }
+        for (int i = 0; i < (ATT_TILE * CH) / ATT_THREADS; ++i) {
+            const int j = j0 + (ATT_THREADS / CH) * i;
+            const int pos = tile * ATT_TILE + j;
+            const bool valid = pos < ctx;
+            const T *src;
+            if (paged) {
+                const int page = pg[w0 + (j >> a.geom.page_shift)];
+                const int slot = pos & (a.geom.page_tokens - 1);
+                src = kv_pool + (valid ? (size_t)page * a.geom.page_elems + kbase + (which ? voff : 0) + (size_t)slot * DH + lcol8 : 0);
+            } else if (which) {
+                const T *vl = reinterpret_cast<const T *>(a.v_lin);
+                src = valid ? vl + (size_t)pos * a.stv + (size_t)hkv * a.shv + lcol8 : vl;
+            } else {
+                const T *kl = reinterpret_cast<const T *>(a.k_lin);
+                src = valid ? kl + (size_t)pos * a.stk + (size_t)hkv * a.shk + lcol8 : kl;
             }
-#pragma unroll
-            for (int g = 0; g < G; ++g) Sp[(hf * G + g) * ATT_TILE + sj] = d[g];
+            cp_async_16(dst + j * ROW + lcol8, src, valid);
         }
+    };
+    fetch_window(tile0);
+    __syncthreads();
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int lrow = lane & 15, lcol = (lane >> 4) * 8;  // ldmatrix.x4 address pattern of this lane
+
+    // One K and one V buffer per CTA, software-pipelined with two cp.async groups per tile: V(t) lands while
+    // the scores and the softmax of tile t run, K(t+1) while the softmax and P.V of tile t run.  Several CTAs
+    // share an SM (shared memory allows 5), which hides what is left.
+    load_rows(tile0, 0);
+    cp_async_commit();
+    load_rows(tile0, 1);
+    cp_async_commit();
+    for (int tile = tile0; tile < tile1; ++tile) {
+        if (paged && tile + 1 < tile1 && (tile + 1 - tile0) % WT == 0) {
+            __syncthreads();  // every copy that reads the old window has been issued
+            fetch_window(tile + 1);
+        }
+        cp_async_wait<1>();  // K(tile) has landed; V(tile) may still be in flight
         __syncthreads();
+
+        // scores of positions [16 warp, 16 warp + 16) for every head slot
+        {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const T *krow = Ks + (warp * 16 + lrow) * ROW + lcol;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t af[4];
+                ldmatrix_x4(af, krow + ks * 16);
+                mma16816<T>(c, af[0], af[1], af[2], af[3], qb[ks][0], qb[ks][1]);
+            }
+            const int h0 = 2 * t4, p0 = warp * 16 + gid;
+            if (h0 < G) {
+                S[h0 * ATT_TILE + p0] = c[0];
+                S[h0 * ATT_TILE + p0 + 8] = c[2];
+            }
+            if (h0 + 1 < G) {
+                S[(h0 + 1) * ATT_TILE + p0] = c[1];
+                S[(h0 + 1) * ATT_TILE + p0 + 8] = c[3];
+            }
+        }
+        __syncthreads();  // scores complete, K buffer free
+        if (tile + 1 < tile1) load_rows(tile + 1, 0);
+        cp_async_commit();
 
         // online softmax, one warp per head
         for (int g = warp; g < G; g += ATT_THREADS / 32) {
             const int p0 = tile * ATT_TILE + lane, p1 = p0 + 32;
-            float s0 = p0 < ctx ? (Sp[g * ATT_TILE + lane] + Sp[(G + g) * ATT_TILE + lane]) * scale : -INFINITY;
-            float s1 = p1 < ctx ? (Sp[g * ATT_TILE + lane + 32] + Sp[(G + g) * ATT_TILE + lane + 32]) * scale : -INFINITY;
+            float s0 = p0 < ctx ? S[g * ATT_TILE + lane] * scale : -INFINITY;
+            float s1 = p1 < ctx ? S[g * ATT_TILE + lane + 32] * scale : -INFINITY;
             float mt = warp_max(fmaxf(s0, s1));
             float mo = m_run[g];
             float mn = fmaxf(mo, mt);
-            float pa = s0 == -INFINITY ? 0.f : expf(s0 - mn);
-            float pb = s1 == -INFINITY ? 0.f : expf(s1 - mn);
-            float sum = warp_sum(pa + pb);
-            S[g * ATT_TILE + lane] = pa;
-            S[g * ATT_TILE + lane + 32] = pb;
+            const T pa = Act<T>::from_f(s0 == -INFINITY ? 0.f : expf(s0 - mn));
+            const T pb = Act<T>::from_f(s1 == -INFINITY ? 0.f : expf(s1 - mn));
+            float sum = warp_sum(Act<T>::to_f(pa) + Act<T>::to_f(pb));
+            Ps[g * PROW + lane] = pa;
+            Ps[g * PROW + lane + 32] = pb;
             if (lane == 0) {
                 float c = mo == -INFINITY ? 0.f : expf(mo - mn);
                 corr[g] = c;
@@ -168,53 +218,56 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
                 m_run[g] = mn;
             }
         }
+        cp_async_wait<1>();  // V(tile) has landed; K(tile + 1) may still be in flight
         __syncthreads();
 
-        // P·V: a thread owns two adjacent dimensions of HG heads; V is read as packed pairs
+        // O += P . V for output dimensions [DW warp, DW warp + DW)
+        {
+            const float cr = gid < G ? corr[gid] : 0.f;
 #pragma unroll
-        for (int i = 0; i < HG; ++i) {
-            const int g = gh * HG + i;
-            if (g < G) {
-                float c = corr[g];
-                float o0 = acc[i][0] * c, o1 = acc[i][1] * c;
-                const float *pr = S + g * ATT_TILE;
-                const T *vcol = vt + 2 * dp;
-#pragma unroll 8
-                for (int j = 0; j < ATT_TILE; ++j) {
-                    float2 v = Act<T>::to_f2(*reinterpret_cast<const uint32_t *>(vcol + j * ROW));
-                    float pj = pr[j];
-                    o0 = fmaf(pj, v.x, o0);
-                    o1 = fmaf(pj, v.y, o1);
+            for (int i = 0; i < NT; ++i) {
+                acc[i][0] *= cr;
+                acc[i][1] *= cr;
+            }
+#pragma unroll
+            for (int ks = 0; ks < ATT_TILE / 16; ++ks) {
+                uint32_t pf[4];
+                ldmatrix_x4(pf, Ps + lrow * PROW + ks * 16 + lcol);
+#pragma unroll
+                for (int np = 0; np < NT / 2; ++np) {
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vf, Vs + (ks * 16 + lrow) * ROW + warp * DW + np * 16 + lcol);
+                    mma16816<T>(acc[2 * np], pf[0], pf[1], pf[2], pf[3], vf[0], vf[1]);
+                    mma16816<T>(acc[2 * np + 1], pf[0], pf[1], pf[2], pf[3], vf[2], vf[3]);
                 }
-                acc[i][0] = o0;
-                acc[i][1] = o1;
             }
         }
-        __syncthreads();
+        __syncthreads();  // V buffer and probabilities free
+        if (tile + 1 < tile1) load_rows(tile + 1, 1);
+        cp_async_commit();
     }
+    cp_async_wait<0>();
 
+    // this thread holds head slot gid, dimensions warp*DW + 8 i + 2 t4 (+1) in acc[i][0..1]
+    const int d0 = warp * DW + 2 * t4;
     T *og = reinterpret_cast<T *>(a.o) + (size_t)t * a.stride_o + (size_t)hkv * G * DH;
     if (my_splits == 1) {
+        if (gid < G) {
+            const float inv = 1.f / l_run[gid];
 #pragma unroll
-        for (int i = 0; i < HG; ++i) {
-            const int g = gh * HG + i;
-            if (g < G) {
-                *reinterpret_cast<uint32_t *>(og + g * DH + 2 * dp) = Act<T>::pack(acc[i][0] / l_run[g], acc[i][1] / l_run[g]);
-            }
+            for (int i = 0; i < NT; ++i)
+                *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(acc[i][0] * inv, acc[i][1] * inv);
         }
         return;
     }
 
     // leave the unnormalised partial and (max, sum); the last split to arrive merges
     const size_t head0 = (size_t)t * a.nh + (size_t)hkv * G;
+    if (gid < G) {
 #pragma unroll
-    for (int i = 0; i < HG; ++i) {
-        const int g = gh * HG + i;
-        if (g < G) {
-            float *dst = a.part_o + ((head0 + g) * a.n_splits + sp) * DH + 2 * dp;
-            dst[0] = acc[i][0];
-            dst[1] = acc[i][1];
-        }
+        for (int i = 0; i < NT; ++i)
+            *reinterpret_cast<float2 *>(a.part_o + ((head0 + gid) * a.n_splits + sp) * DH + d0 + 8 * i) =
+                make_float2(acc[i][0], acc[i][1]);
     }
     if (tid < G) {
         a.part_ml[((head0 + tid) * a.n_splits + sp) * 2] = m_run[tid];
@@ -229,24 +282,28 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    if (gid < G) {
+        const float *ml = a.part_ml + (head0 + gid) * a.n_splits * 2;
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, __ldcg(ml + 2 * s2));
+        float L = 0.f, O[NT][2];
 #pragma unroll
-    for (int i = 0; i < HG; ++i) {
-        const int g = gh * HG + i;
-        if (g < G) {
-            const float *ml = a.part_ml + (head0 + g) * a.n_splits * 2;
-            float M = -INFINITY;
-            for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, __ldcg(ml + 2 * s2));
-            float L = 0.f, O0 = 0.f, O1 = 0.f;
-            for (int s2 = 0; s2 < my_splits; ++s2) {
-                float ms = __ldcg(ml + 2 * s2), ls = __ldcg(ml + 2 * s2 + 1);
-                float w = ms == -INFINITY ? 0.f : expf(ms - M);
-                L = fmaf(ls, w, L);
-                float2 o = __ldcg(reinterpret_cast<const float2 *>(a.part_o + ((head0 + g) * a.n_splits + s2) * DH + 2 * dp));
-                O0 = fmaf(o.x, w, O0);
-                O1 = fmaf(o.y, w, O1);
+        for (int i = 0; i < NT; ++i) O[i][0] = O[i][1] = 0.f;
+        for (int s2 = 0; s2 < my_splits; ++s2) {
+            float ms = __ldcg(ml + 2 * s2), ls = __ldcg(ml + 2 * s2 + 1);
+            float w = ms == -INFINITY ? 0.f : expf(ms - M);
+            L = fmaf(ls, w, L);
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                float2 o = __ldcg(reinterpret_cast<const float2 *>(a.part_o + ((head0 + gid) * a.n_splits + s2) * DH + d0 + 8 * i));
+                O[i][0] = fmaf(o.x, w, O[i][0]);
+                O[i][1] = fmaf(o.y, w, O[i][1]);
             }
-            *reinterpret_cast<uint32_t *>(og + g * DH + 2 * dp) = Act<T>::pack(O0 / L, O1 / L);
         }
+        const float inv = 1.f / L;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+            *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(O[i][0] * inv, O[i][1] * inv);
     }
     if (tid == 0) a.counters[(size_t)t * a.nkvh + hkv] = 0;  // ready for the next launch
 }
@@ -275,8 +332,8 @@ void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok) {
 template <class T, int DH, int G>
 static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = attn_kernel<T, DH, G>;
-    size_t smem = (size_t)2 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)G * DH * sizeof(T) +
-                  (size_t)(3 * G * ATT_TILE + 3 * G) * sizeof(float);
+    size_t smem = (size_t)2 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)16 * (ATT_TILE + 8) * sizeof(T) +
+                  (size_t)(G * ATT_TILE + 3 * G) * sizeof(float);
     static std::mutex mu;
     static std::map<int, bool> done;
     int dev = 0;

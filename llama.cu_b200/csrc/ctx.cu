@@ -176,7 +176,7 @@ static void attn_plan(const lcu_ctx *c, int n_tok, int *n_splits, int *tps) {
         *tps = max_tiles;
         return;
     }
-    int t = env_tps > 0 ? env_tps : (ctas * 2 >= sm_count() ? 2 : 1);
+    int t = env_tps > 0 ? env_tps : (ctas * 2 >= sm_count() ? 4 : 1);
     int z = (max_tiles + t - 1) / t;
     int z_cap = 2048 / n_tok;  // bounds the partial-output scratch
     if (z_cap > 64) z_cap = 64;

@@ -233,8 +233,11 @@ def test_attention_kv_cached(L, O, dt, nh, nkvh, dh, pos, seq):
     vc[pos:pos + seq] = v
     want = O.attention(q, kc[:pos + seq], vc[:pos + seq], nh, nkvh, dh, pos, dt)
     got = as_f32(ot)
+    # The kernel rounds the probabilities to the activation dtype before the P.V product (tensor-core operands,
+    # as a GEMM-based operator that keeps the attention matrix in f16 does); that adds at most ulp/2 * sum p|v|
+    # to an output element, which matters where the output itself is close to zero: hence the 0.25 floor.
     ulp = 2.0 ** (-10 if dt == 0 else -7)
-    assert np.all(np.abs(got - want) <= 2 * ulp * np.maximum(np.abs(want), 1e-2) + 1e-5), np.abs(got - want).max()
+    assert np.all(np.abs(got - want) <= 2 * ulp * np.maximum(np.abs(want), 0.25)), np.abs(got - want).max()
     # the append half
     assert np.array_equal(as_f32(cache[pos:pos + seq, 0]), k) and np.array_equal(as_f32(cache[pos:pos + seq, 1]), v)
 
