@@ -83,8 +83,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t r[16]) {
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t r[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+
+constexpr int TC_MAX_STAGES = 12;
+
 struct TcShared {
-    unsigned long long full[8], empty[8], tmem_full[2], tmem_empty[2];
+    unsigned long long full[TC_MAX_STAGES], empty[TC_MAX_STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
     int last;
@@ -173,8 +181,8 @@ __device__ __forceinline__ void tc_finish(const GemvArgs &a, int n, int first, f
 template <class T>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               int n_pairs, int N, int n_stages, int ksplit, int vec, uint32_t idesc, float *ws, unsigned *tickets,
-               uint32_t *status) {
+               int n_pairs, int N, int n_stages, int units_per_cta, int max_seg, int vec, uint32_t idesc, float *ws,
+               unsigned *tickets, uint32_t *status) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment: the 128-byte swizzle pattern repeats every 8 rows = 1024 bytes
     unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
@@ -183,12 +191,16 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)TC_BM * (N + 1) * 4);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int Kper = a.in / ksplit, nkb = Kper / TC_BK;
+    const int nkb = a.in / TC_BK;  // K blocks of a whole row block
     const bool swiglu = a.epilogue == EPI_SWIGLU;
     const int acc_cols = N < 32 ? 32 : N;      // TMEM columns of one accumulator
     const int tm_cols = 2 * acc_cols;          // two accumulators
     const int n_rb = (n_pairs + 63) / 64;
-    const int n_tiles = n_rb * ksplit;
+    // work units = (row block, K block) pairs in row-block-major order; this CTA owns a contiguous range and
+    // walks it as segments that end at row-block boundaries (stream-K)
+    const int total_units = n_rb * nkb;
+    const int u_begin = min(total_units, (int)blockIdx.x * units_per_cta);
+    const int u_end = min(total_units, u_begin + units_per_cta);
 
     if (tid == 0) {
         for (int i = 0; i < n_stages; ++i) {
@@ -216,12 +228,13 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
         // ---------------- TMA producer
         grid_dep_wait();
         int it = 0;  // stages issued so far (all tiles)
-        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x) {
-            const int rb = tile / ksplit, ks = tile - rb * ksplit;
+        for (int u = u_begin; u < u_end && !sh->abort_flag;) {
+            const int rb = u / nkb, kb0 = u - rb * nkb;
+            const int kb1 = min(nkb, kb0 + (u_end - u));
+            u += kb1 - kb0;
             const int row_a = swiglu ? rb * 64 : rb * TC_BM;
             const int row_b = swiglu ? a.di + rb * 64 : rb * TC_BM + 64;
-            const int k0 = ks * Kper;
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int slot = it % n_stages;
                 const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
                 if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
@@ -232,7 +245,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 const uint32_t bar = tc_smem(&sh->full[slot]);
                 const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
                 tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
-                const int kx = k0 + kb * TC_BK;
+                const int kx = kb * TC_BK;
                 tc_tma_2d(dst, &map_w, kx, row_a, bar);
                 tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, row_b, bar);
                 tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
@@ -241,7 +254,10 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer
         int it = 0, ti = 0;
-        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x, ++ti) {
+        for (int u = u_begin; u < u_end && !sh->abort_flag; ++ti) {
+            const int rb = u / nkb, kb0 = u - rb * nkb;
+            const int kb1 = min(nkb, kb0 + (u_end - u));
+            u += kb1 - kb0;
             const int ab = ti & 1;
             // the epilogue must have drained this accumulator (two tiles ago)
             if (!tc_mbar_wait(tc_smem(&sh->tmem_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, &sh->abort_flag)) {
@@ -251,7 +267,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t d_tmem = tmem + (uint32_t)(ab * acc_cols);
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int slot = it % n_stages;
                 const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
                 if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
@@ -263,7 +279,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TC_A_BYTES;
 #pragma unroll
                 for (int k = 0; k < TC_BK / 16; ++k)
-                    tc_mma_f16(d_tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_mma_f16(d_tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                 tc_commit(tc_smem(&sh->empty[slot]));  // the stage is free once these MMAs have read it
             }
             tc_commit(tc_smem(&sh->tmem_full[ab]));     // accumulator complete
@@ -274,8 +290,14 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
         const int q = warp & 3;                      // a warp may only touch TMEM lanes [32q, 32q + 32)
         const int row = q * 32 + lane;
         int ti = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
-            const int rb = tile / ksplit, ks = tile - rb * ksplit;
+        for (int u = u_begin; u < u_end; ++ti) {
+            const int rb = u / nkb, kb0 = u - rb * nkb;
+            const int kb1 = min(nkb, kb0 + (u_end - u));
+            u += kb1 - kb0;
+            const bool whole = kb0 == 0 && kb1 == nkb;  // this CTA holds the complete sum of the row block
+            // otherwise: CTAs first_cta .. last_cta share the row block, in K order
+            const int first_cta = (rb * nkb) / units_per_cta, last_cta = (rb * nkb + nkb - 1) / units_per_cta;
+            const int n_seg = last_cta - first_cta + 1, seg = (int)blockIdx.x - first_cta;
             const int ab = ti & 1;
             bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[ab]), (uint32_t)(ti >> 1) & 1u, &sh->abort_flag);
             if (!ok) {
@@ -299,7 +321,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
             }
             if (!ok) break;
             const int items = 64 * N;
-            if (ksplit == 1 && vec) {
+            if (whole && vec) {
                 // (token, 8 outputs) items; residual vectors are fetched first, then everything is stored
                 const int chunks = swiglu ? 8 : 16;
                 TcPre pre[8];
@@ -322,7 +344,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                     }
                     tc_finish<T>(a, n, first, v, u, pre[cnt]);
                 }
-            } else if (ksplit == 1) {
+            } else if (whole) {
                 for (int idx = et; idx < items; idx += 128) {
                     int j = idx / N, n = idx - j * N;
                     int p = rb * 64 + j;
@@ -330,9 +352,10 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                     int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
                     gemv_epilogue<T>(a, p, n, stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
                 }
-            } else if (vec) {
-                // split-K, vector form.  Partial tiles go to scratch token-major, 128 floats per (split, row
-                // block, token); the CTA that takes the last ticket sums them in split order and finishes.
+            } else {
+                // the row block is shared (the host only cuts row blocks when the vector epilogue applies).  Partial
+                // tiles go to scratch token-major, 128 floats per (row block, segment, token); the CTA that takes
+                // the last ticket sums them in K order and finishes.
                 for (int idx = et; idx < 16 * N; idx += 128) {
                     int c = idx & 15, n = idx >> 4;
                     if (n >= a.n_tok) continue;
@@ -341,7 +364,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                     lo.z = stg[(8 * c + 2) * (N + 1) + n]; lo.w = stg[(8 * c + 3) * (N + 1) + n];
                     hi.x = stg[(8 * c + 4) * (N + 1) + n]; hi.y = stg[(8 * c + 5) * (N + 1) + n];
                     hi.z = stg[(8 * c + 6) * (N + 1) + n]; hi.w = stg[(8 * c + 7) * (N + 1) + n];
-                    float *dst = ws + (((size_t)ks * n_rb + rb) * N + n) * TC_BM + 8 * c;
+                    float *dst = ws + (((size_t)rb * max_seg + seg) * N + n) * TC_BM + 8 * c;
                     __stcg(reinterpret_cast<float4 *>(dst), lo);
                     __stcg(reinterpret_cast<float4 *>(dst + 4), hi);
                 }
@@ -349,7 +372,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (et == 0) {
                     unsigned ticket = atomicAdd(&tickets[rb], 1u);
-                    sh->last = ticket == (unsigned)ksplit - 1;
+                    sh->last = ticket == (unsigned)n_seg - 1;
                     if (sh->last) tickets[rb] = 0;
                 }
                 asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -370,8 +393,8 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                         if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
                         float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
-                        for (int s2 = 0; s2 < ksplit; ++s2) {
-                            const float *src = ws + (((size_t)s2 * n_rb + rb) * N + n) * TC_BM + 8 * c;
+                        for (int s2 = 0; s2 < n_seg; ++s2) {
+                            const float *src = ws + (((size_t)rb * max_seg + s2) * N + n) * TC_BM + 8 * c;
                             float4 lo = __ldcg(reinterpret_cast<const float4 *>(src));
                             float4 hi = __ldcg(reinterpret_cast<const float4 *>(src + 4));
                             v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
@@ -386,43 +409,199 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                         tc_finish<T>(a, n, first, v, u, pre[cnt]);
                     }
                 }
-            } else {
-                for (int idx = et; idx < items; idx += 128) {
-                    int j = idx / N, n = idx - j * N;
-                    int p = rb * 64 + j;
-                    if (p >= n_pairs) continue;
-                    int ra = swiglu ? j : 2 * j, rb2 = swiglu ? 64 + j : 2 * j + 1;
-                    float2 v = make_float2(stg[ra * (N + 1) + n], stg[rb2 * (N + 1) + n]);
-                    *reinterpret_cast<float2 *>(ws + (((size_t)ks * n_pairs + p) * N + n) * 2) = v;
-                }
-                __threadfence();
-                asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (et == 0) {
-                    unsigned ticket = atomicAdd(&tickets[rb], 1u);
-                    sh->last = ticket == (unsigned)ksplit - 1;
-                    if (sh->last) tickets[rb] = 0;
-                }
-                asm volatile("bar.sync 2, 128;" ::: "memory");
-                if (sh->last) {
-                    __threadfence();
-                    for (int idx = et; idx < items; idx += 128) {
-                        int j = idx / N, n = idx - j * N;
-                        int p = rb * 64 + j;
-                        if (p >= n_pairs || n >= a.n_tok) continue;
-                        float va = 0.f, vb = 0.f;
-                        for (int s2 = 0; s2 < ksplit; ++s2) {
-                            float2 v = __ldcg(reinterpret_cast<const float2 *>(ws + (((size_t)s2 * n_pairs + p) * N + n) * 2));
-                            va += v.x;
-                            vb += v.y;
-                        }
-                        gemv_epilogue<T>(a, p, n, va, vb);
-                    }
-                }
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");  // staging buffer is reused by the next tile
         }
     }
     // ---------------- tail: everyone meets, then the allocating warp returns the TMEM columns
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    p2p_signal(a.push);  // no-op without tensor parallelism
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tm_cols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ tokens-on-M form
+// D[128 token lanes x BN weight rows] += X[128 x 64] . W_tile[BN x 64]^T: the token block (<= 64 real rows, the
+// rest of the 128-row operand is never read back) is the M side and a tile of BN weight rows the N side.  BN is
+// a free multiple of 16, so the row dimension of ANY matrix of the model cuts into enough equal tiles to keep
+// all SMs busy (no K splitting, no partial sums through scratch), and a TMEM lane holds consecutive outputs
+// of ONE token: the epilogue goes straight from tcgen05.ld registers to 16-byte stores.
+//   SwiGLU tiles hold BN/2 gate rows followed by their BN/2 up rows (two TMA boxes).
+// Measured result: correct, but slower than the row-block form for the tile heights that balance the 8B
+// shapes (BN = 32..48): every MMA re-reads the whole 128-row activation operand from shared memory (4 KB per
+// K = 16 step although at most 64 rows are real), i.e. about 5 bytes of shared-memory reads per weight byte
+// at BN = 32, and the kernel becomes shared-memory-bandwidth bound (8B batch-32 step 7.4 ms against 5.2 ms).
+// It is kept behind LCU_TC_LAYOUT=tokens; an M = 64 variant would halve that overhead.
+constexpr int TCN_A_BYTES = 128 * TC_BK * 2;  // activation operand region of a stage (128 rows x 128 bytes)
+
+template <class T>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcn_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                int n_tiles, int Nbox, int BN, int n_stages, int tm_cols, uint32_t idesc, uint32_t *status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    const int stage_bytes = TCN_A_BYTES + BN * 128;
+    TcShared *sh = reinterpret_cast<TcShared *>(smem + (size_t)n_stages * stage_bytes);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nkb = a.in / TC_BK;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+    const int BP = BN / 2;  // SwiGLU: pairs per tile
+
+    if (tid == 0) {
+        for (int i = 0; i < n_stages; ++i) {
+            tc_mbar_init(tc_smem(&sh->full[i]), 1);
+            tc_mbar_init(tc_smem(&sh->empty[i]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(tc_smem(&sh->tmem_full[i]), 1);
+            tc_mbar_init(tc_smem(&sh->tmem_empty[i]), 1);
+        }
+        sh->abort_flag = 0;
+        sh->last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // rows of the activation operand that no TMA box ever fills: keep them zero (their products are never read)
+    for (int st = 0; st < n_stages; ++st) {
+        uint4 *p = reinterpret_cast<uint4 *>(smem + (size_t)st * stage_bytes + (size_t)Nbox * 128);
+        for (int i = tid; i < (128 - Nbox) * 8; i += TC_THREADS) p[i] = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)), "r"(tm_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer
+        grid_dep_wait();
+        int it = 0;
+        const uint32_t tx = (uint32_t)(Nbox * 128 + BN * 128);
+        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x) {
+            const int row_a = swiglu ? tile * BP : tile * BN;
+            const int row_b = a.di + tile * BP;  // SwiGLU only
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int slot = it % n_stages;
+                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
+                if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
+                    atomicOr(status, 4u);
+                    sh->abort_flag = 1;
+                    break;
+                }
+                const uint32_t bar = tc_smem(&sh->full[slot]);
+                const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+                tc_mbar_expect_tx(bar, tx);
+                const int kx = kb * TC_BK;
+                tc_tma_2d(dst, &map_x, kx, 0, bar);
+                tc_tma_2d(dst + TCN_A_BYTES, &map_w, kx, row_a, bar);
+                if (swiglu) tc_tma_2d(dst + TCN_A_BYTES + BP * 128, &map_w, kx, row_b, bar);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        int it = 0, ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x, ++ti) {
+            const int ab = ti & 1;
+            if (!tc_mbar_wait(tc_smem(&sh->tmem_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t d_tmem = tmem + (uint32_t)(ab * (tm_cols / 2));
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int slot = it % n_stages;
+                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
+                if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
+                    atomicOr(status, 4u);
+                    sh->abort_flag = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TCN_A_BYTES;
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    tc_mma_f16(d_tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit(tc_smem(&sh->empty[slot]));
+            }
+            tc_commit(tc_smem(&sh->tmem_full[ab]));
+        }
+    } else if (warp >= 2) {
+        // ---------------- epilogue warps: lane = token, columns = consecutive outputs of that token
+        const int et = tid - 64;
+        const int q = warp & 3;  // a warp may only touch TMEM lanes [32q, 32q + 32)
+        const int n = q * 32 + lane;
+        const bool warp_active = q * 32 < a.n_tok;
+        const bool tok = n < a.n_tok;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
+            const int ab = ti & 1;
+            bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[ab]), (uint32_t)(ti >> 1) & 1u, &sh->abort_flag);
+            if (!ok) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok && warp_active) {
+                const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * (tm_cols / 2));
+                if (swiglu) {
+                    for (int c0 = 0; c0 < BP; c0 += 8) {
+                        uint32_t g[8], up[8];
+                        tc_ld8(tbase + (uint32_t)c0, g);
+                        tc_ld8(tbase + (uint32_t)(BP + c0), up);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        const int first = tile * BP + c0;
+                        if (tok && first + 8 <= a.di) {
+                            float v[8], u[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                v[i] = __uint_as_float(g[i]);
+                                u[i] = __uint_as_float(up[i]);
+                            }
+                            TcPre pre;
+                            tc_finish<T>(a, n, first, v, u, pre);
+                        }
+                    }
+                } else {
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        uint32_t r[16];
+                        tc_ld16(tbase + (uint32_t)c0, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        const int first = tile * BN + c0;
+                        TcPre pre[2];
+                        const bool v0 = tok && first + 8 <= a.out, v1 = tok && first + 16 <= a.out;
+                        if (v0) tc_prefetch<T>(a, n, first, pre[0]);
+                        if (v1) tc_prefetch<T>(a, n, first + 8, pre[1]);
+                        float v[8], u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (v0) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+                            tc_finish<T>(a, n, first, v, u, pre[0]);
+                        }
+                        if (v1) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 + i]);
+                            tc_finish<T>(a, n, first + 8, v, u, pre[1]);
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (et == 0) {  // the accumulator may be overwritten from here on
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&sh->tmem_empty[ab])) : "memory");
+            }
+            if (!ok) break;
+        }
+    }
+    // ---------------- tail
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     p2p_signal(a.push);  // no-op without tensor parallelism
     __syncthreads();
@@ -500,27 +679,6 @@ static size_t tc_smem_bytes(int N, int stages) {
     return 1024 + (size_t)stages * (TC_A_BYTES + N * 128) + (size_t)TC_BM * (N + 1) * 4 + sizeof(TcShared) + 64;
 }
 
-// K splits: tiles are dealt round-robin to the persistent CTAs, so what matters is that the tile count
-// divides well over the SMs; fewer splits win ties (partial sums cost scratch traffic).
-static int tc_choose_ksplit(int in, int n_pairs, int N) {
-    const int row_blocks = (n_pairs + 63) / 64;
-    const int sms = sm_count();
-    int best = 1;
-    double best_eff = -1.0;
-    for (int ks = 1; ks <= 16; ks *= 2) {
-        if (in % (ks * TC_BK) || in / ks < 2 * TC_BK) break;
-        if (ks > 1 && (!g_tc_ws || (size_t)ks * row_blocks * 64 * N * 2 * 4 > g_tc_ws_bytes || row_blocks > g_tc_n_tickets)) break;
-        if (ks > 1 && row_blocks * (ks / 2) >= sms) break;  // split only while the SMs are not all busy
-        int tiles = row_blocks * ks;
-        int rounds = (tiles + sms - 1) / sms;
-        double eff = (double)tiles / ((double)rounds * sms);
-        if (tiles < sms) eff = (double)tiles / sms;
-        eff -= 0.02 * (ks > 1) + 0.01 * (ks > 2) + 0.01 * (ks > 4) + 0.02 * (ks > 8);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
-    }
-    return best;
-}
-
 template <class T>
 static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = gemm_tc_kernel<T>;
@@ -538,6 +696,7 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         auto it = done.find(dev);
         if (it == done.end()) {
             LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            LCU_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             void *p = nullptr;
             LCU_CHECK_CUDA(cudaGetSymbolAddress(&p, g_tc_fallback_status));
             it = done.emplace(dev, reinterpret_cast<uint32_t *>(p)).first;
@@ -546,17 +705,10 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     }
     if (dry) return LCU_OK;
     const int n_pairs = a.out / 2;
-    CUtensorMap mw, mx;
-    int rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, 64);
-    if (rc) return rc;
-    // the activation map has exactly n_tok rows: the rest of the N-row box is out of bounds and zero-filled
-    rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
-    if (rc) return rc;
-    const int ksplit = tc_choose_ksplit(a.in, n_pairs, N);
+    const int sms = sm_count();
     const uint32_t fmt = dt == LCU_BF16 ? 1u : 0u;
-    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-    const int n_tiles = ((n_pairs + 63) / 64) * ksplit;
-    dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
+    CUtensorMap mw, mx;
+    int rc;
     // 16-byte epilogue accesses need aligned, 8-divisible outputs
     bool vec_ok = a.stride_y % 8 == 0 && ((uintptr_t)a.y % 16) == 0 && (a.epilogue == EPI_SWIGLU ? a.di % 8 == 0 : a.out % 8 == 0);
     if (a.epilogue == EPI_RESIDUAL) vec_ok = vec_ok && a.stride_res % 8 == 0 && ((uintptr_t)a.res % 16) == 0;
@@ -564,8 +716,70 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         vec_ok = vec_ok && a.dh % 8 == 0 && a.qd % 8 == 0 && a.kvd % 8 == 0 && ((uintptr_t)a.kv_pool % 16) == 0 &&
                  ((uintptr_t)a.sin_t % 16) == 0 && ((uintptr_t)a.cos_t % 16) == 0;
     const int vec = vec_ok ? 1 : 0;
-    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, ksplit, vec, idesc,
-                                 g_tc_ws, g_tc_tickets, status));
+    // opt-in (LCU_TC_LAYOUT=tokens): measured slower than the row-block form on the 8B shapes, see the kernel's header
+    static const bool tokens_on_m = getenv("LCU_TC_LAYOUT") && getenv("LCU_TC_LAYOUT")[0] == 't';
+    if (vec && tokens_on_m) {
+        // ---- tokens on M: pick the tile height BN (weight rows, a multiple of 16) that finishes soonest when the
+        // tiles are dealt round-robin to the SMs: rounds x BN, larger BN on ties (fewer activation re-reads)
+        static const int env_bn = getenv("LCU_TC_BN") ? atoi(getenv("LCU_TC_BN")) : 0;
+        const bool swiglu = a.epilogue == EPI_SWIGLU;
+        const int rows = swiglu ? a.di : a.out;  // rows (pairs for SwiGLU) to cover; a SwiGLU tile of BN holds BN/2 pairs
+        int best_bn = 0;
+        long best_cost = -1;
+        for (int bn = 32; bn <= 128; bn += 16) {
+            if (env_bn) bn = env_bn;
+            const int per = swiglu ? bn / 2 : bn;
+            const int tiles = (rows + per - 1) / per;
+            const long cost = (long)((tiles + sms - 1) / sms) * bn;
+            if (best_cost < 0 || cost <= best_cost) {
+                best_cost = cost;
+                best_bn = bn;
+            }
+            if (env_bn) break;
+        }
+        const int BN = best_bn, per = swiglu ? BN / 2 : BN;
+        LCU_REQUIRE(BN >= 16 && BN <= 128 && BN % 16 == 0, "gemm_tc: tile height %d", BN);
+        const int n_tiles = (rows + per - 1) / per;
+        const int stage_bytes = TCN_A_BYTES + BN * 128;
+        int stages = (int)(((size_t)227 * 1024 - 1024 - sizeof(TcShared) - 64) / stage_bytes);
+        if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+        const size_t smem_n = 1024 + (size_t)stages * stage_bytes + sizeof(TcShared) + 64;
+        int tm_cols = 32;
+        while (tm_cols < 2 * BN) tm_cols *= 2;
+        rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, (uint32_t)per);
+        if (rc) return rc;
+        rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
+        if (rc) return rc;
+        const uint32_t idesc_n = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        dim3 grid(n_tiles < sms ? n_tiles : sms);
+        LCU_CHECK_CUDA(launch_kernel(gemm_tcn_kernel<T>, grid, dim3(TC_THREADS), smem_n, s, pdl, a, mw, mx, n_tiles, N, BN, stages,
+                                     tm_cols, idesc_n, status));
+        g_linear_last_ctas = (int)grid.x;
+        return LCU_OK;
+    }
+    // ---- weight rows on M (any output shape; row blocks of 128)
+    rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, 64);
+    if (rc) return rc;
+    // the activation map has exactly n_tok rows: the rest of the N-row box is out of bounds and zero-filled
+    rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
+    if (rc) return rc;
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    // Work split (stream-K): the (row block, K block) units are dealt to the SMs in equal contiguous ranges, so
+    // the launch is balanced whatever the row-block count; row blocks cut between CTAs are summed through scratch.
+    // Without scratch, or when the vector epilogue does not apply, ranges are whole row blocks.
+    const int n_rb = (n_pairs + 63) / 64, nkb = a.in / TC_BK, total = n_rb * nkb;
+    int units = (total + sms - 1) / sms;
+    if (units < 8) units = 8;  // at least 8 K blocks (128 KB of weights) per CTA
+    int max_seg = (nkb + units - 1) / units + 1;
+    const bool cut = vec && g_tc_ws && g_tc_tickets && n_rb <= g_tc_n_tickets &&
+                     (size_t)n_rb * max_seg * N * TC_BM * 4 <= g_tc_ws_bytes;
+    if (!cut || units % nkb == 0) {
+        units = nkb * ((n_rb + sms - 1) / sms);
+        max_seg = 1;
+    }
+    dim3 grid((total + units - 1) / units);
+    LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(TC_THREADS), smem, s, pdl, a, mw, mx, n_pairs, N, stages, units, max_seg, vec,
+                                 idesc, g_tc_ws, g_tc_tickets, status));
     g_linear_last_ctas = (int)grid.x;
     return LCU_OK;
 }
