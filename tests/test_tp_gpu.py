@@ -55,3 +55,17 @@ def test_tp2_matches_tp1_and_oracle(L, O, name, layers, vocab, tmp_path):
         if got["ids"] == o_ids:
             assert np.abs(np.array(got["logits_last"]) - want).max() <= tol
     assert two["launches"] > one["launches"]  # the all-reduces are part of the step
+    # wider groups, peer-memory transport only (as many as the box has GPUs and the KV heads divide)
+    for world in (4, 8):
+        if torch.cuda.device_count() < world or cfg.nkvh % world or cfg.nh % world:
+            continue
+        wide = run_world(world, name, layers, vocab, steps, tmp_path, "p2p")
+        assert wide["p2p"] and wide["status"] == 0
+        for i in range(3):
+            for s in range(steps):
+                if wide["ids"][i][s] != o_ids[i][s]:
+                    lg = np.sort(o_lgs[i][s])
+                    assert lg[-1] - lg[-2] <= 2 * tol, (world, i, s)
+                    break
+        if wide["ids"] == o_ids:
+            assert np.abs(np.array(wide["logits_last"]) - want).max() <= tol
