@@ -378,35 +378,75 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (sh->last) {
                     __threadfence();
-                    const int chunks = swiglu ? 8 : 16;
-                    TcPre pre[8];
-                    int cnt = 0;
-                    for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
-                        int c = idx % chunks, n = idx / chunks;
-                        int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
-                        if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
-                    }
-                    cnt = 0;
-                    for (int idx = et; idx < chunks * N; idx += 128, ++cnt) {
-                        int c = idx % chunks, n = idx / chunks;
-                        int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
-                        if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
-                        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-                        for (int s2 = 0; s2 < n_seg; ++s2) {
-                            const float *src = ws + (((size_t)rb * max_seg + s2) * N + n) * TC_BM + 8 * c;
-                            float4 lo = __ldcg(reinterpret_cast<const float4 *>(src));
-                            float4 hi = __ldcg(reinterpret_cast<const float4 *>(src + 4));
-                            v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
-                            v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
-                            if (swiglu) {
-                                float4 l2 = __ldcg(reinterpret_cast<const float4 *>(src + 64));
-                                float4 h2 = __ldcg(reinterpret_cast<const float4 *>(src + 68));
-                                u[0] += l2.x; u[1] += l2.y; u[2] += l2.z; u[3] += l2.w;
-                                u[4] += h2.x; u[5] += h2.y; u[6] += h2.z; u[7] += h2.w;
+                    // Merge of the segments' partial sums.  A partial row lives in the L2 slice of whichever SM wrote
+                    // it and one dependent round trip costs more than a microsecond here, so the loads of up to 6
+                    // segments for TWO rows of 8 floats are all issued before the first add (96 registers of loads in
+                    // flight per thread; the epilogue warps have registers to spare), the adds then run in K order.
+                    // Measured: 11 us -> see the profile for a 6-segment merge of a 128 x 32 tile.
+                    const size_t seg_stride = (size_t)N * TC_BM;
+                    auto merge2 = [&](const float *r0, const float *r1, float o0[8], float o1[8]) {
+                        float4 b0[12], b1[12];
+#pragma unroll
+                        for (int s2 = 0; s2 < 6; ++s2) {
+                            if (s2 < n_seg) {
+                                b0[2 * s2] = __ldcg(reinterpret_cast<const float4 *>(r0 + s2 * seg_stride));
+                                b0[2 * s2 + 1] = __ldcg(reinterpret_cast<const float4 *>(r0 + s2 * seg_stride + 4));
+                                b1[2 * s2] = __ldcg(reinterpret_cast<const float4 *>(r1 + s2 * seg_stride));
+                                b1[2 * s2 + 1] = __ldcg(reinterpret_cast<const float4 *>(r1 + s2 * seg_stride + 4));
                             }
                         }
-                        tc_finish<T>(a, n, first, v, u, pre[cnt]);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o0[i] = o1[i] = 0.f;
+#pragma unroll
+                        for (int s2 = 0; s2 < 6; ++s2) {
+                            if (s2 < n_seg) {
+                                o0[0] += b0[2 * s2].x; o0[1] += b0[2 * s2].y; o0[2] += b0[2 * s2].z; o0[3] += b0[2 * s2].w;
+                                o0[4] += b0[2 * s2 + 1].x; o0[5] += b0[2 * s2 + 1].y; o0[6] += b0[2 * s2 + 1].z; o0[7] += b0[2 * s2 + 1].w;
+                                o1[0] += b1[2 * s2].x; o1[1] += b1[2 * s2].y; o1[2] += b1[2 * s2].z; o1[3] += b1[2 * s2].w;
+                                o1[4] += b1[2 * s2 + 1].x; o1[5] += b1[2 * s2 + 1].y; o1[6] += b1[2 * s2 + 1].z; o1[7] += b1[2 * s2 + 1].w;
+                            }
+                        }
+                        for (int s2 = 6; s2 < n_seg; ++s2) {  // more than 6 CTAs on one row block: small launches only
+                            const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(r0 + s2 * seg_stride));
+                            const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(r0 + s2 * seg_stride + 4));
+                            const float4 c0 = __ldcg(reinterpret_cast<const float4 *>(r1 + s2 * seg_stride));
+                            const float4 c1 = __ldcg(reinterpret_cast<const float4 *>(r1 + s2 * seg_stride + 4));
+                            o0[0] += a0.x; o0[1] += a0.y; o0[2] += a0.z; o0[3] += a0.w; o0[4] += a1.x; o0[5] += a1.y; o0[6] += a1.z; o0[7] += a1.w;
+                            o1[0] += c0.x; o1[1] += c0.y; o1[2] += c0.z; o1[3] += c0.w; o1[4] += c1.x; o1[5] += c1.y; o1[6] += c1.z; o1[7] += c1.w;
+                        }
+                    };
+                    const float *tile0 = ws + (size_t)rb * max_seg * seg_stride;
+                    const float zero8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    if (swiglu) {
+                        // one item (8 pairs of one token) per pass: its gate row and its up row
+                        for (int idx = et; idx < 8 * N; idx += 128) {
+                            const int c = idx & 7, n = idx >> 3;
+                            const int first = rb * 64 + 8 * c;
+                            if (!(n < a.n_tok && first + 8 <= a.di)) continue;
+                            float g8[8], u8[8];
+                            const float *r = tile0 + (size_t)n * TC_BM + 8 * c;
+                            merge2(r, r + 64, g8, u8);
+                            TcPre pre;
+                            tc_finish<T>(a, n, first, g8, u8, pre);
+                        }
+                    } else {
+                        // two items per pass: 8 consecutive rows of token n and of token n + 8 (idx and idx + 128)
+                        for (int idx = et; idx < 16 * N; idx += 256) {
+                            const int c = idx & 15, n0 = idx >> 4, n1 = n0 + 8;
+                            const int first = rb * TC_BM + 8 * c;
+                            const bool rows_ok = first + 8 <= a.out;
+                            const bool v0 = rows_ok && n0 < a.n_tok, v1 = rows_ok && n1 < a.n_tok && idx + 128 < 16 * N;
+                            if (!v0 && !v1) continue;
+                            TcPre pre0, pre1;
+                            if (v0) tc_prefetch<T>(a, n0, first, pre0);
+                            if (v1) tc_prefetch<T>(a, n1, first, pre1);
+                            float o0[8], o1[8];
+                            const float *r0 = tile0 + (size_t)(v0 ? n0 : n1) * TC_BM + 8 * c;
+                            const float *r1 = tile0 + (size_t)(v1 ? n1 : n0) * TC_BM + 8 * c;
+                            merge2(r0, r1, o0, o1);
+                            if (v0) tc_finish<T>(a, n0, first, o0, zero8, pre0);
+                            if (v1) tc_finish<T>(a, n1, first, o1, zero8, pre1);
+                        }
                     }
                 }
             }

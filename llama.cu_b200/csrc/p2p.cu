@@ -135,12 +135,11 @@ int p2p_reduce_launch(P2pState &st, void *y, size_t elems, int dt, unsigned expe
     if (grid > 64) grid = 64;
     unsigned *header = reinterpret_cast<unsigned *>(st.own);
     if (dt == LCU_BF16)
-        p2p_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(header, st.parity, src, st.n, reinterpret_cast<__nv_bfloat16 *>(y),
-                                                              n_vec, expected, status);
+        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src, st.n,
+                                     reinterpret_cast<__nv_bfloat16 *>(y), n_vec, expected, status));
     else
-        p2p_reduce_kernel<__half><<<grid, 256, 0, s>>>(header, st.parity, src, st.n, reinterpret_cast<__half *>(y), n_vec,
-                                                       expected, status);
-    LCU_CHECK_CUDA(cudaGetLastError());
+        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__half>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src, st.n,
+                                     reinterpret_cast<__half *>(y), n_vec, expected, status));
     st.parity ^= 1;
     return LCU_OK;
 }
@@ -150,8 +149,8 @@ int p2p_broadcast_launch(P2pState &st, void *data, size_t bytes, int root, uint3
     LCU_REQUIRE(bytes % 4 == 0 && 256 + bytes <= st.hdr_bytes, "p2p broadcast: %zu bytes do not fit the buffer", bytes);
     BcastDst peers;
     for (int r = 0; r < P2P_MAX_RANKS; ++r) peers.base[r] = r < st.n ? reinterpret_cast<unsigned char *>(st.base[r]) : nullptr;
-    p2p_broadcast_kernel<<<1, 256, 0, s>>>(peers, st.n, st.rank, root, reinterpret_cast<uint32_t *>(data), (int)(bytes / 4), status);
-    LCU_CHECK_CUDA(cudaGetLastError());
+    LCU_CHECK_CUDA(launch_kernel(p2p_broadcast_kernel, dim3(1), dim3(256), 0, s, false, peers, st.n, st.rank, root,
+                                 reinterpret_cast<uint32_t *>(data), (int)(bytes / 4), status));
     return LCU_OK;
 }
 
