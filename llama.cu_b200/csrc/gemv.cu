@@ -44,7 +44,7 @@ __device__ __forceinline__ void vec8_to_f32(const uint4 &v, float f[8]) {
 }
 
 template <class T, bool Q8, int NT, int KI, int RP>
-__global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int RS, int n_pairs) {
+__global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(const GemvArgs a, int KS, int RS, int n_pairs) {
     constexpr int R = 2 * RP;
     constexpr int VE = Q8 ? 16 : 8;  // weights per 16-byte vector
     extern __shared__ __align__(16) unsigned char smem[];
@@ -88,11 +88,16 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
         }
     };
 
-    // weights do not depend on the previous kernel: start streaming before the wait
-    if (a.early_prefetch && n_groups > 0) load_group(0);
+    // Order of the first requests matters: L1 hands data back in request order, so activations asked for AFTER the
+    // first weight group would only arrive with it (about 3 us under full load) and the RMSNorm arithmetic would then
+    // run with the memory pipe idle.  The activations are therefore requested first, as asynchronous copies straight
+    // into shared memory (no registers held), the first weight group right behind them, and the norm is computed
+    // while those weights are in flight.  early_prefetch == 3 keeps the older order (weights, then activations).
+    const bool x_first = a.early_prefetch == 1;
+    if (a.early_prefetch == 3 && n_groups > 0) load_group(0);
     if (a.pdl_trigger == 0) grid_dep_launch();
     grid_dep_wait();
-    if (!a.early_prefetch && n_groups > 0) load_group(0);
+    if (a.early_prefetch == 0 && n_groups > 0) load_group(0);
 
     // ---- stage the activations (optionally RMS-normalised) in shared memory
     {
@@ -103,10 +108,22 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvArgs a, int KS, int
             if (t < a.n_tok) {
                 size_t row = a.x_rows ? a.x_rows[t] : (size_t)t;
                 const uint4 *src = reinterpret_cast<const uint4 *>(xg + row * a.stride_x);
-                for (int i = threadIdx.x; i < nv8; i += blockDim.x) dst[i] = src[i];
+                if (x_first) {
+                    for (int i = threadIdx.x; i < nv8; i += blockDim.x) {
+                        unsigned d = (unsigned)__cvta_generic_to_shared(dst + i);
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + i) : "memory");
+                    }
+                } else {
+                    for (int i = threadIdx.x; i < nv8; i += blockDim.x) dst[i] = src[i];
+                }
             } else {
                 for (int i = threadIdx.x; i < nv8; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
             }
+        }
+        if (x_first) {
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (n_groups > 0) load_group(0);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
         if (a.prologue == PRO_RMSNORM) {
