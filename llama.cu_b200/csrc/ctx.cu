@@ -414,9 +414,9 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
         // the batched (tensor-core) form of the linear layers
         c->batched_ok = gemm_skinny_supported(d.d, q8) && gemm_skinny_supported(c->qd, q8) && gemm_skinny_supported(c->di_l, q8);
         if (c->batched_ok) {
-            rc = gemm_skinny_warm(d.d, c->qd + 2 * c->kvd, c->dt);
-            if (!rc) rc = gemm_skinny_warm(c->qd, d.d, c->dt);
-            if (!rc) rc = gemm_skinny_warm(c->di_l, d.d, c->dt);
+            rc = gemm_skinny_warm(d.d, c->qd + 2 * c->kvd, c->dt, q8);
+            if (!rc) rc = gemm_skinny_warm(c->qd, d.d, c->dt, q8);
+            if (!rc) rc = gemm_skinny_warm(c->di_l, d.d, c->dt, q8);
             if (!rc) rc = gemm_skinny_warm(d.d, d.vocab & ~1, c->dt);
             if (!rc && gemm_tc_supported(d.d, q8)) rc = gemm_tc_warm(c->dt);
             if (rc) {

@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <map>
 #include <mutex>
+#include <type_traits>
 
 #include "gemv.cuh"
 
@@ -43,7 +44,24 @@ __device__ __forceinline__ void sk_cp_async_16(void *smem_dst, const void *gsrc,
 // grid = (row blocks of 64 pairs, K splits).  With more than one K split the partial sums go through
 // `ws` [split][pair][token][2] and the last CTA of a row block to arrive (ticket) adds them in split
 // order and runs the epilogue, so the result does not depend on which CTA finishes last.
-template <class T, int NTL>
+// int8 x 4 -> two f16x2 without I2F: bytes xor 0x80 land in the mantissa of 1024.0 (0x64xx = 1024 + byte),
+// minus 1152 gives the signed value exactly.
+__device__ __forceinline__ void q8x4_to_h2(uint32_t q, uint32_t &h01, uint32_t &h23) {
+    const uint32_t u = q ^ 0x80808080u;
+    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));
+    uint32_t ua = __byte_perm(u, 0x64646464u, 0x4140), ub = __byte_perm(u, 0x64646464u, 0x4342);
+    __half2 a = __hsub2(*reinterpret_cast<__half2 *>(&ua), bias);
+    __half2 b = __hsub2(*reinterpret_cast<__half2 *>(&ub), bias);
+    h01 = *reinterpret_cast<uint32_t *>(&a);
+    h23 = *reinterpret_cast<uint32_t *>(&b);
+}
+
+// Q8 = true (f16 activations only): weights are the repacked Q8_0 planes, int8 [out, in] then f16 scales
+// [out, in/32].  Inside a 64-wide K block lane t4 owns k = 8 t4 .. 8 t4 + 7 of EACH 32-wide quantisation block
+// (two 8-byte loads per row), so every pair of MMAs stays inside one quantisation block: its products are summed
+// exactly (integers times f16 activations, f32 accumulation) into a temporary accumulator which is then scaled
+// by the block's scale of row g / row g + 8 — the same arithmetic as scale * q dequantised in f32.
+template <class T, int NTL, bool Q8>
 __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_kernel(const GemvArgs a, int n_pairs, float *ws,
                                                                     unsigned *tickets) {
     constexpr int N = 8 * NTL;
@@ -66,8 +84,14 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
     const unsigned char *wbase = reinterpret_cast<const unsigned char *>(a.w);
     // inside a 64-wide K block lane t4 owns K values [16*t4, 16*t4 + 16): one 256-bit load per row,
     // and the 4 lanes of a quad read one full 128-byte line
-    const unsigned char *wa = wbase + (pv ? ra : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
-    const unsigned char *wb = wbase + (pv ? rb : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
+    const unsigned char *wa = Q8 ? wbase + (pv ? ra : 0) * (size_t)a.in + (size_t)k0 + 8 * t4
+                                 : wbase + (pv ? ra : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
+    const unsigned char *wb = Q8 ? wbase + (pv ? rb : 0) * (size_t)a.in + (size_t)k0 + 8 * t4
+                                 : wbase + (pv ? rb : 0) * (size_t)a.in * 2 + ((size_t)k0 + 16 * t4) * 2;
+    // Q8: the 8 scales of a 256-wide chunk are 16 contiguous bytes per row
+    const uint16_t *sbase = reinterpret_cast<const uint16_t *>(a.w_scales);
+    const uint16_t *sa = Q8 ? sbase + (pv ? ra : 0) * (size_t)(a.in / 32) + k0 / 32 : nullptr;
+    const uint16_t *sb = Q8 ? sbase + (pv ? rb : 0) * (size_t)(a.in / 32) + k0 / 32 : nullptr;
     const T *xg = reinterpret_cast<const T *>(a.x);
 
     float acc[NTL][4];
@@ -87,14 +111,27 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
     };
     // weights: a rolling window of SK_KBC 64-wide blocks per row in registers; block kb of the next
     // chunk is requested as soon as block kb of this chunk has been multiplied
-    u32x8 wra[SK_KBC], wrb[SK_KBC];
+    u32x8 wra[Q8 ? 1 : SK_KBC], wrb[Q8 ? 1 : SK_KBC];
+    uint2 qa[Q8 ? SK_KBC : 1][2], qb[Q8 ? SK_KBC : 1][2];  // Q8: [64-block][quantisation block] 8 int8 each
+    uint4 sca = make_uint4(0, 0, 0, 0), scb = sca, sca_n = sca, scb_n = sca;  // Q8: 8 f16 scales of this / the next chunk
     auto load_w = [&](int c, int kb) {
         int kk = c * SK_XK + kb * 64;
         bool v = pv && kk < Kper;
-        u32x8 z;
-        z.lo = z.hi = make_uint4(0, 0, 0, 0);
-        wra[kb] = v ? ld_stream_256(wa + (size_t)kk * 2) : z;
-        wrb[kb] = v ? ld_stream_256(wb + (size_t)kk * 2) : z;
+        if constexpr (Q8) {
+            qa[kb][0] = v ? ld_stream_64(wa + kk) : make_uint2(0, 0);
+            qa[kb][1] = v ? ld_stream_64(wa + kk + 32) : make_uint2(0, 0);
+            qb[kb][0] = v ? ld_stream_64(wb + kk) : make_uint2(0, 0);
+            qb[kb][1] = v ? ld_stream_64(wb + kk + 32) : make_uint2(0, 0);
+            if (kb == 0) {
+                sca_n = v ? __ldg(reinterpret_cast<const uint4 *>(sa + kk / 32)) : make_uint4(0, 0, 0, 0);
+                scb_n = v ? __ldg(reinterpret_cast<const uint4 *>(sb + kk / 32)) : make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            u32x8 z;
+            z.lo = z.hi = make_uint4(0, 0, 0, 0);
+            wra[kb] = v ? ld_stream_256(wa + (size_t)kk * 2) : z;
+            wrb[kb] = v ? ld_stream_256(wb + (size_t)kk * 2) : z;
+        }
     };
 #pragma unroll
     for (int kb = 0; kb < SK_KBC; ++kb) load_w(0, kb);
@@ -107,17 +144,48 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
-        const unsigned char *xs = smem + (size_t)(c & 1) * N * ROWB + (size_t)t4 * 32;
+        const unsigned char *xs = smem + (size_t)(c & 1) * N * ROWB + (size_t)t4 * (Q8 ? 16 : 32);
+        if constexpr (Q8) {
+            sca = sca_n;
+            scb = scb_n;
+        }
 #pragma unroll
         for (int kb = 0; kb < SK_KBC; ++kb) {
+            if constexpr (Q8) {
+                const uint32_t sw_a[4] = {sca.x, sca.y, sca.z, sca.w}, sw_b[4] = {scb.x, scb.y, scb.z, scb.w};
 #pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xs + (size_t)(nt * 8 + g) * ROWB + kb * 128);
-                const uint4 x0 = xp[0], x1 = xp[1];
-                mma16816<T>(acc[nt], wra[kb].lo.x, wrb[kb].lo.x, wra[kb].lo.y, wrb[kb].lo.y, x0.x, x0.y);
-                mma16816<T>(acc[nt], wra[kb].lo.z, wrb[kb].lo.z, wra[kb].lo.w, wrb[kb].lo.w, x0.z, x0.w);
-                mma16816<T>(acc[nt], wra[kb].hi.x, wrb[kb].hi.x, wra[kb].hi.y, wrb[kb].hi.y, x1.x, x1.y);
-                mma16816<T>(acc[nt], wra[kb].hi.z, wrb[kb].hi.z, wra[kb].hi.w, wrb[kb].hi.w, x1.z, x1.w);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t af[4], bf[4];
+                    q8x4_to_h2(qa[kb][h].x, af[0], af[1]);
+                    q8x4_to_h2(qa[kb][h].y, af[2], af[3]);
+                    q8x4_to_h2(qb[kb][h].x, bf[0], bf[1]);
+                    q8x4_to_h2(qb[kb][h].y, bf[2], bf[3]);
+                    // scale of quantisation block 2 kb + h of this chunk: half (2 kb + h) of the 8 loaded
+                    const __half2 pa = *reinterpret_cast<const __half2 *>(&sw_a[kb]);
+                    const __half2 pb = *reinterpret_cast<const __half2 *>(&sw_b[kb]);
+                    const float fa = h ? __high2float(pa) : __low2float(pa), fb = h ? __high2float(pb) : __low2float(pb);
+#pragma unroll
+                    for (int nt = 0; nt < NTL; ++nt) {
+                        const uint4 xv = *reinterpret_cast<const uint4 *>(xs + (size_t)(nt * 8 + g) * ROWB + kb * 128 + h * 64);
+                        float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma16816<T>(tmp, af[0], bf[0], af[1], bf[1], xv.x, xv.y);
+                        mma16816<T>(tmp, af[2], bf[2], af[3], bf[3], xv.z, xv.w);
+                        acc[nt][0] = fmaf(fa, tmp[0], acc[nt][0]);
+                        acc[nt][1] = fmaf(fa, tmp[1], acc[nt][1]);
+                        acc[nt][2] = fmaf(fb, tmp[2], acc[nt][2]);
+                        acc[nt][3] = fmaf(fb, tmp[3], acc[nt][3]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NTL; ++nt) {
+                    const uint4 *xp = reinterpret_cast<const uint4 *>(xs + (size_t)(nt * 8 + g) * ROWB + kb * 128);
+                    const uint4 x0 = xp[0], x1 = xp[1];
+                    mma16816<T>(acc[nt], wra[kb].lo.x, wrb[kb].lo.x, wra[kb].lo.y, wrb[kb].lo.y, x0.x, x0.y);
+                    mma16816<T>(acc[nt], wra[kb].lo.z, wrb[kb].lo.z, wra[kb].lo.w, wrb[kb].lo.w, x0.z, x0.w);
+                    mma16816<T>(acc[nt], wra[kb].hi.x, wrb[kb].hi.x, wra[kb].hi.y, wrb[kb].hi.y, x1.x, x1.y);
+                    mma16816<T>(acc[nt], wra[kb].hi.z, wrb[kb].hi.z, wra[kb].hi.w, wrb[kb].hi.w, x1.z, x1.w);
+                }
             }
             if (c + 1 < nch) load_w(c + 1, kb);
         }
@@ -176,7 +244,7 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
 
 // ------------------------------------------------------------------ host side
 
-bool gemm_skinny_supported(int in, int w_q8) { return !w_q8 && in >= SK_XK && in % 32 == 0; }
+bool gemm_skinny_supported(int in, int w_q8) { return in >= SK_XK && in % 32 == 0 && (!w_q8 || in % SK_XK == 0); }
 
 // Scratch for split-K partial sums and the per-row-block tickets, handed over by the context.
 static thread_local float *g_ws = nullptr;
@@ -209,9 +277,9 @@ static int sk_choose_ksplit(int in, int n_pairs, int n) {
     return best;
 }
 
-template <class T, int NTL>
+template <class T, int NTL, bool Q8>
 static int sk_inst(const GemvArgs &a, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
-    auto kernel = gemm_skinny_kernel<T, NTL>;
+    auto kernel = gemm_skinny_kernel<T, NTL, Q8>;
     constexpr int N = 8 * NTL;
     size_t smem = (size_t)2 * N * (SK_XK * 2 + 16);
     static std::mutex mu;
@@ -227,6 +295,7 @@ static int sk_inst(const GemvArgs &a, int n_pairs, cudaStream_t s, bool pdl, boo
     }
     if (dry) return LCU_OK;
     int ksplit = sk_choose_ksplit(a.in, n_pairs, N);
+    if (Q8) while (ksplit > 1 && (a.in / ksplit) % SK_XK) ksplit /= 2;  // a K range must hold whole scale groups
     dim3 grid((n_pairs + SK_BP - 1) / SK_BP, ksplit);
     LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(SK_THREADS), smem, s, pdl, a, n_pairs, g_ws, g_tickets));
     g_linear_last_ctas = (int)(grid.x * grid.y);
@@ -237,10 +306,22 @@ template <class T>
 static int sk_t(const GemvArgs &a, cudaStream_t s, bool pdl, bool dry) {
     int n_pairs = a.out / 2;
     int ntl = a.n_tok <= 16 ? 2 : (a.n_tok <= 32 ? 4 : 8);
+    if (a.w_q8) {
+        if constexpr (std::is_same<T, __half>::value) {
+            switch (ntl) {
+            case 2: return sk_inst<T, 2, true>(a, n_pairs, s, pdl, dry);
+            case 4: return sk_inst<T, 4, true>(a, n_pairs, s, pdl, dry);
+            default: return sk_inst<T, 8, true>(a, n_pairs, s, pdl, dry);
+            }
+        } else {
+            set_error("gemm_skinny: Q8_0 weights need f16 activations");
+            return LCU_ERR_INVALID;
+        }
+    }
     switch (ntl) {
-    case 2: return sk_inst<T, 2>(a, n_pairs, s, pdl, dry);
-    case 4: return sk_inst<T, 4>(a, n_pairs, s, pdl, dry);
-    default: return sk_inst<T, 8>(a, n_pairs, s, pdl, dry);
+    case 2: return sk_inst<T, 2, false>(a, n_pairs, s, pdl, dry);
+    case 4: return sk_inst<T, 4, false>(a, n_pairs, s, pdl, dry);
+    default: return sk_inst<T, 8, false>(a, n_pairs, s, pdl, dry);
     }
 }
 
@@ -257,11 +338,11 @@ int gemm_skinny_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     return LCU_ERR_INVALID;
 }
 
-int gemm_skinny_warm(int in, int out, int dt) {
-    if (!gemm_skinny_supported(in, 0)) return LCU_OK;
+int gemm_skinny_warm(int in, int out, int dt, int w_q8) {
+    if (!gemm_skinny_supported(in, w_q8)) return LCU_OK;
     for (int n = 16; n <= 64; n *= 2) {
         GemvArgs a{};
-        a.in = in; a.out = out; a.n_tok = n; a.stride_x = in; a.epilogue = EPI_STORE;
+        a.in = in; a.out = out; a.n_tok = n; a.stride_x = in; a.epilogue = EPI_STORE; a.w_q8 = w_q8;
         int rc = gemm_skinny_launch(a, dt, nullptr, false, true);
         if (rc) return rc;
     }

@@ -133,7 +133,7 @@ int gemv_warm(int in, int out, bool q8, int dt);
 // activations must be prepared (no RMSNorm prologue, no row gather).
 bool gemm_skinny_supported(int in, int w_q8);
 int gemm_skinny_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
-int gemm_skinny_warm(int in, int out, int dt);
+int gemm_skinny_warm(int in, int out, int dt, int w_q8 = 0);
 // Split-K scratch (f32 partial sums) and zeroed tickets (one per 128-row block) for the calling thread.
 void gemm_skinny_set_scratch(void *ws, size_t ws_bytes, unsigned *tickets, int n_tickets);
 // tcgen05 / TMEM / TMA form of the batched kernel (gemm_tc.cu): same arguments.

@@ -183,8 +183,10 @@ def test_linear_batched_tensor_core(L, O, dt, n, k, out, res):
     assert (got == want).mean() > 0.85  # same value except where the summation order flips a rounding
 
 
-@pytest.mark.parametrize("n,k,out", [(1, 4096, 256), (2, 14336, 64), (4, 256, 128), (1, 1024, 6144)])
+@pytest.mark.parametrize("n,k,out", [(1, 4096, 256), (2, 14336, 64), (4, 256, 128), (1, 1024, 6144),
+                                     (5, 256, 128), (16, 4096, 512), (33, 14336, 256), (64, 1024, 640), (100, 2048, 130)])
 def test_linear_q8_0(L, O, n, k, out):
+    """1..4 rows: GEMV with in-register dequantisation; more: the mma.sync kernel with per-block scaling."""
     from llama_cu_b200.model import q8_0_blocks
     rng = np.random.default_rng(k)
     x, xt = rand_act(rng, (n, k), 0, O)
@@ -204,7 +206,7 @@ def test_linear_q8_0(L, O, n, k, out):
     assert np.array_equal(w, np.repeat(sc.astype(np.float32), 32, axis=1) * q.astype(np.float32))
     want = O.linear(x, w, None, 0)
     got = as_f32(yt)
-    assert np.all(np.abs(got - want) <= 2.0 ** -10 * np.maximum(np.abs(want), 1e-2) + 1e-6)
+    assert np.all(np.abs(got - want) <= 2.0 ** -10 * np.maximum(np.abs(want), 1e-2) + 1e-6), np.abs(got - want).max()
 
 
 @pytest.mark.parametrize("dt", [0, 1])
