@@ -26,6 +26,7 @@ WORKLOADS = {
     "llama8b-q8_0-b1": ("llama8b_q8", 1, (128, 128)),
     "llama8b-q8_0-b16": ("llama8b_q8", 16, (128, 128)),
     "llama70b-f16-b64": ("llama70b", 64, (1024, 1024)),
+    "llama70b-tp8shard-f16-b64": ("llama70b_tp8shard", 64, (1024, 1024)),  # one rank's share, for profiling
     "tiny-f16-b1": ("tiny", 1, (16, 16)),
 }
 DEFAULT_WORKLOAD = "llama8b-f16-b1"

@@ -166,7 +166,11 @@ __device__ __forceinline__ void tc_finish(const GemvArgs &a, int n, int first, f
     uint4 o;
     o.x = Act<T>::pack(v[0], v[1]); o.y = Act<T>::pack(v[2], v[3]); o.z = Act<T>::pack(v[4], v[5]); o.w = Act<T>::pack(v[6], v[7]);
     if (a.push.n && (a.epilogue == EPI_STORE || a.epilogue == EPI_RESIDUAL)) {
-        // tensor parallelism: the partial goes to every rank's all-reduce slot over peer memory
+        // tensor parallelism: the partial goes to the owner's (scatter form) or every rank's all-reduce slot over peer memory
+        if (a.push.scatter_cols) {
+            *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.push.slot[first / a.push.scatter_cols]) + (size_t)n * a.stride_y + first) = o;
+            return;
+        }
         for (int k = 0; k < a.push.n; ++k)
             *reinterpret_cast<uint4 *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)n * a.stride_y + first) = o;
         return;
@@ -810,6 +814,9 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     const int n_rb = (n_pairs + 63) / 64, nkb = a.in / TC_BK, total = n_rb * nkb;
     int units = (total + sms - 1) / sms;
     if (units < 8) units = 8;  // at least 8 K blocks (128 KB of weights) per CTA
+    // a row block is shared by at most 6 CTAs: the merge loads 6 segments at once, beyond that it walks them one
+    // round trip at a time (a [1280 x 8192] projection cut 15 ways took 41 us for 21 MB)
+    if (units < (nkb + 4) / 5) units = (nkb + 4) / 5;
     int max_seg = (nkb + units - 1) / units + 1;
     const bool cut = vec && g_tc_ws && g_tc_tickets && n_rb <= g_tc_n_tickets &&
                      (size_t)n_rb * max_seg * N * TC_BM * 4 <= g_tc_ws_bytes;

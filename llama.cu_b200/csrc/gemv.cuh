@@ -64,6 +64,10 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         size_t r = (size_t)pair * 2;
         if (a.push.n) {
             const uint32_t packed = Act<T>::pack(va, vb);
+            if (a.push.scatter_cols) {
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[r / a.push.scatter_cols]) + (size_t)t * a.stride_y + r) = packed;
+                break;
+            }
             for (int k = 0; k < a.push.n; ++k)
                 *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)t * a.stride_y + r) = packed;
             break;
@@ -80,6 +84,10 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         float2 rf = Act<T>::to_f2(rr);
         const uint32_t packed = Act<T>::pack(va + rf.x, vb + rf.y);
         if (a.push.n) {
+            if (a.push.scatter_cols) {
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[r / a.push.scatter_cols]) + (size_t)t * a.stride_y + r) = packed;
+                break;
+            }
             for (int k = 0; k < a.push.n; ++k)
                 *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)t * a.stride_y + r) = packed;
             break;

@@ -68,6 +68,88 @@ __global__ void __launch_bounds__(256) p2p_reduce_kernel(unsigned *header, int p
     }
 }
 
+struct GatherDst {
+    unsigned char *gather[P2P_MAX_RANKS];  // every rank's gather buffer of this parity
+    unsigned *garrive[P2P_MAX_RANKS];      // every rank's second counter of this parity
+};
+
+// Scatter form: this rank owns columns [rank * cols, (rank + 1) * cols) of every token row.
+template <class T>
+__global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(unsigned *header, int parity, ReduceSrc src, GatherDst dst,
+                                                                 int n_ranks, int rank, T *y, int n_tok, int d, int cols,
+                                                                 unsigned expected, uint32_t *status) {
+    unsigned *arrive = header + parity, *leave = header + 2 + parity, *garrive = header + 5 + parity;
+    const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : P2P_WAIT_CYCLES;
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        while (ld_acquire_sys(arrive) < expected) {
+            if (clock64() - t0 > limit) {
+                atomicOr(status, 16u);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    // phase A: sum my column slice of every token, store it into every rank's gather buffer
+    const int vec_per_row = cols / 8;
+    const size_t n_vec = (size_t)n_tok * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / vec_per_row), v = (int)(i - (size_t)t * vec_per_row);
+        const size_t off = ((size_t)t * d + (size_t)rank * cols) / 8 + v;  // in 16-byte vectors
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 vv[P2P_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < P2P_MAX_RANKS; ++r)
+            if (r < n_ranks) vv[r] = __ldcg(reinterpret_cast<const uint4 *>(src.slot[r]) + off);
+#pragma unroll
+        for (int r = 0; r < P2P_MAX_RANKS; ++r) {
+            if (r < n_ranks) {
+                const float2 a = Act<T>::to_f2(vv[r].x), b = Act<T>::to_f2(vv[r].y), c = Act<T>::to_f2(vv[r].z),
+                             e = Act<T>::to_f2(vv[r].w);
+                acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+                acc[4] += c.x; acc[5] += c.y; acc[6] += e.x; acc[7] += e.y;
+            }
+        }
+        uint4 o;
+        o.x = Act<T>::pack(acc[0], acc[1]); o.y = Act<T>::pack(acc[2], acc[3]);
+        o.z = Act<T>::pack(acc[4], acc[5]); o.w = Act<T>::pack(acc[6], acc[7]);
+#pragma unroll
+        for (int r = 0; r < P2P_MAX_RANKS; ++r)
+            if (r < n_ranks) reinterpret_cast<uint4 *>(dst.gather[r])[off] = o;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < (unsigned)n_ranks) atomicAdd_system(dst.garrive[threadIdx.x], 1u);
+    // phase B: every owner's every CTA has delivered -> copy the gathered rows to the residual stream
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        const unsigned want = (unsigned)n_ranks * gridDim.x;
+        while (ld_acquire_sys(garrive) < want) {
+            if (clock64() - t0 > limit) {
+                atomicOr(status, 16u);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    const uint4 *g = reinterpret_cast<const uint4 *>(dst.gather[rank]);
+    const size_t all_vec = (size_t)n_tok * d / 8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < all_vec; i += (size_t)gridDim.x * blockDim.x)
+        reinterpret_cast<uint4 *>(y)[i] = __ldcg(g + i);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(leave, 1u);
+        if (t == gridDim.x - 1) {
+            *reinterpret_cast<volatile unsigned *>(leave) = 0u;
+            *reinterpret_cast<volatile unsigned *>(arrive) = 0u;
+            *reinterpret_cast<volatile unsigned *>(garrive) = 0u;
+            __threadfence();
+        }
+    }
+}
+
 struct BcastDst {
     unsigned char *base[P2P_MAX_RANKS];
 };
@@ -109,31 +191,60 @@ __global__ void __launch_bounds__(256) p2p_broadcast_kernel(BcastDst peers, int 
 
 size_t p2p_header_bytes(size_t bcast_bytes) { return (256 + bcast_bytes + 255) / 256 * 256; }
 size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes) {
-    return p2p_header_bytes(bcast_bytes) + (size_t)2 * n_ranks * slot_bytes;
+    return p2p_header_bytes(bcast_bytes) + (size_t)2 * n_ranks * slot_bytes + (size_t)2 * slot_bytes;
 }
 
 static inline unsigned char *slot_ptr(void *base, const P2pState &st, int parity, int src) {
     return reinterpret_cast<unsigned char *>(base) + st.hdr_bytes + ((size_t)parity * st.n + src) * st.slot_bytes;
 }
 
-void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push) {
+static inline unsigned char *gather_ptr(void *base, const P2pState &st, int parity) {
+    return reinterpret_cast<unsigned char *>(base) + st.hdr_bytes + ((size_t)2 * st.n + parity) * st.slot_bytes;
+}
+
+void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push, int scatter_cols) {
     push->n = st.n;
+    push->scatter_cols = scatter_cols;
     for (int r = 0; r < P2P_MAX_RANKS; ++r) {
         push->slot[r] = r < st.n ? slot_ptr(st.base[r], st, st.parity, st.rank) + byte_off : nullptr;
         push->arrive[r] = r < st.n ? reinterpret_cast<unsigned *>(st.base[r]) + st.parity : nullptr;
     }
 }
 
-int p2p_reduce_launch(P2pState &st, void *y, size_t elems, int dt, unsigned expected, uint32_t *status, cudaStream_t s) {
+int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned expected, int scatter_cols, uint32_t *status,
+                      cudaStream_t s) {
+    const size_t elems = (size_t)n_tok * d;
     LCU_REQUIRE(st.ready, "p2p all-reduce: peers are not attached");
     LCU_REQUIRE(elems % 8 == 0 && elems * 2 <= st.slot_bytes, "p2p all-reduce: %zu elements do not fit the slot", elems);
     ReduceSrc src;
     for (int r = 0; r < P2P_MAX_RANKS; ++r)
         src.slot[r] = r < st.n ? slot_ptr(st.own, st, st.parity, r) : nullptr;
+    unsigned *header = reinterpret_cast<unsigned *>(st.own);
+    if (scatter_cols) {
+        LCU_REQUIRE(scatter_cols * st.n == d && scatter_cols % 8 == 0, "p2p all-reduce: %d columns per rank do not tile d = %d", scatter_cols, d);
+        GatherDst dst;
+        for (int r = 0; r < P2P_MAX_RANKS; ++r) {
+            dst.gather[r] = r < st.n ? gather_ptr(st.base[r], st, st.parity) : nullptr;
+            dst.garrive[r] = r < st.n ? reinterpret_cast<unsigned *>(st.base[r]) + 5 + st.parity : nullptr;
+        }
+        const size_t n_vec = (size_t)n_tok * scatter_cols / 8;
+        int grid = (int)((n_vec + 255) / 256);
+        if (grid > 32) grid = 32;
+        if (grid < 1) grid = 1;
+        if (dt == LCU_BF16)
+            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, false, header, st.parity,
+                                         src, dst, st.n, st.rank, reinterpret_cast<__nv_bfloat16 *>(y), n_tok, d, scatter_cols,
+                                         expected, status));
+        else
+            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__half>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src,
+                                         dst, st.n, st.rank, reinterpret_cast<__half *>(y), n_tok, d, scatter_cols, expected,
+                                         status));
+        st.parity ^= 1;
+        return LCU_OK;
+    }
     const size_t n_vec = elems / 8;
     int grid = (int)((n_vec + 255) / 256);
     if (grid > 64) grid = 64;
-    unsigned *header = reinterpret_cast<unsigned *>(st.own);
     if (dt == LCU_BF16)
         LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src, st.n,
                                      reinterpret_cast<__nv_bfloat16 *>(y), n_vec, expected, status));

@@ -11,6 +11,12 @@
 //   * a small local kernel on each rank waits (bounded) until its counter reaches
 //     n_ranks x producer CTAs, sums the n_ranks slots in rank order in f32, rounds once and writes
 //     the residual stream; the last of its CTAs to leave zeroes the counter.
+// Large rounds (scatter form): pushing every partial to every rank costs (n_ranks - 1) x the message
+// per rank on NVLink.  Instead rank k OWNS columns [k d/n, (k+1) d/n): producers store a partial only
+// into the owner's region, the owner's kernel sums its column slice and stores the result into the
+// "gather" buffer of every rank, raises their second counter, waits for its own second counter
+// (every owner, every CTA) and copies the gathered rows to the residual stream: 2 (n-1)/n of the
+// message per rank instead of (n-1), for one more hop.
 // Two parities alternate from one all-reduce to the next.  A rank can only push into parity p again
 // after it has passed its own reduction of parity p^1, which needs every rank's push of p^1, which
 // every rank issues after finishing its reduction of p: so a slot and its counter are never written
@@ -30,6 +36,7 @@ struct P2pPush {
     void *slot[P2P_MAX_RANKS];          // slot (parity, me) in rank r's region, offset like `y`
     unsigned *arrive[P2P_MAX_RANKS];    // rank r's arrival counter of this parity
     int n;
+    int scatter_cols;                   // 0: store to every rank; else columns per owner, store to rank col / scatter_cols
 };
 
 #ifdef __CUDACC__
@@ -52,15 +59,18 @@ struct P2pState {
     bool ready = false;
 };
 
-// Region layout: words 0..1 arrival counters, 2..3 departure tickets (per parity), 4 broadcast flag;
-// from byte 256 the broadcast buffer (bcast_bytes); from hdr_bytes the slots.
+// Region layout: words 0..1 arrival counters, 2..3 departure tickets (per parity), 4 broadcast flag, 5..6 second
+// (gather) counters; from byte 256 the broadcast buffer (bcast_bytes); from hdr_bytes the slots
+// [2][n_ranks][slot_bytes], then the gather buffers [2][slot_bytes].
 size_t p2p_header_bytes(size_t bcast_bytes);
 size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes);
-// Fills `push` for the next all-reduce (current parity) with a byte offset into the slot.
-void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push);
-// Enqueues the local reduction: waits for `expected` arrivals, y[i] = sum over ranks of slot r, elems of
-// the 2-byte activation type; then flips the parity.  status: device word that gets bit 16 on a timed-out wait.
-int p2p_reduce_launch(P2pState &st, void *y, size_t elems, int dt, unsigned expected, uint32_t *status, cudaStream_t s);
+// Fills `push` for the next all-reduce (current parity) with a byte offset into the slot; scatter_cols as in P2pPush.
+void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push, int scatter_cols = 0);
+// Enqueues the local reduction of n_tok rows of d elements (2-byte activation type): waits for `expected` arrivals,
+// y = sum over ranks of the slots (scatter_cols != 0: the scatter form above); then flips the parity.
+// status: device word that gets bit 16 on a timed-out wait.
+int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned expected, int scatter_cols, uint32_t *status,
+                      cudaStream_t s);
 
 // Token broadcast from rank `root` (the reference's `share_inputs`, exec/engine.rs:264-274): the root stores
 // `bytes` (a multiple of 4, at most the broadcast buffer) into every other rank's buffer and raises their flag;

@@ -63,6 +63,9 @@ CONFIGS = {
     "llama8b": ModelConfig("llama8b", 32, 4096, 32, 8, 128, 14336, 128256, 5e5, F16, nctx=2048),
     "llama8b_q8": ModelConfig("llama8b_q8", 32, 4096, 32, 8, 128, 14336, 128256, 5e5, F16, Q8_0, nctx=2048),
     "llama70b": ModelConfig("llama70b", 80, 8192, 64, 8, 128, 28672, 32000, 1e4, F16, nctx=2048),
+    # what ONE rank of the 70B shape computes under 8-way tensor parallelism (8 query heads, 1 KV head, 3584 FFN
+    # columns; no all-reduce): a single-GPU stand-in for profiling the per-rank kernels
+    "llama70b_tp8shard": ModelConfig("llama70b_tp8shard", 80, 8192, 8, 1, 128, 3584, 32000, 1e4, F16, nctx=2048),
 }
 
 
