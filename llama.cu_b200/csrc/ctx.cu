@@ -688,6 +688,10 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     // short kernels on B200 (3.8 ms vs 3.3 ms per 8B step), so it is off unless LCU_PDL=1.
     static const bool pdl = getenv("LCU_PDL") && getenv("LCU_PDL")[0] == '1';
     static const int pdl_trigger = getenv("LCU_PDL_TRIGGER") ? atoi(getenv("LCU_PDL_TRIGGER")) : 2;
+    // programmatic dependent launch on selected edges of a layer only (bit 0: QKV -> attention, 1: attention -> O,
+    // 2: O -> gate|up, 3: gate|up -> down, 4: down -> next QKV): the successor is launched with the attribute and the
+    // predecessor releases it as soon as all its CTAs are running
+    static const int pdl_edges = getenv("LCU_PDL_EDGES") ? atoi(getenv("LCU_PDL_EDGES")) : 28;
     static const int early_prefetch = getenv("LCU_PREFETCH") ? atoi(getenv("LCU_PREFETCH")) : 1;
     int launches = 0;
     unsigned char *D = c->desc_dev;
@@ -750,7 +754,9 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     c->p2p.parity = 0;  // every step holds an even number of all-reduces, so captured graphs agree on it
     int linear_ctas = 0;  // CTAs of the launches of the last `linear` call
     auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
-                      const void *norm_w, bool push = false) -> int {
+                      const void *norm_w, bool push = false, int edge_in = -1, int edge_out = -1) -> int {
+        const bool pdl_in = pdl || (edge_in >= 0 && ((pdl_edges >> edge_in) & 1));
+        const int trig = (edge_out >= 0 && ((pdl_edges >> edge_out) & 1)) ? 0 : pdl_trigger;
         linear_ctas = 0;
         const void *src = xin;
         int src_stride = stride_in;
@@ -779,11 +785,13 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (a.pos) { a.pos += t0; a.tok_seq += t0; }
             if (!batched && norm) { a.prologue = PRO_RMSNORM; a.norm_w = norm_w; a.norm_f32 = norm_dt == LCU_F32; a.eps = d.eps; }
             else a.prologue = PRO_NONE;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
+            a.pdl_trigger = trig;
+            // launched early: the first weights are requested before waiting for the predecessor, then the activations
+            a.early_prefetch = (pdl_in && early_prefetch == 1) ? 3 : early_prefetch;
             if (push) p2p_make_push(c->p2p, (size_t)t0 * stride_out * eb, &a.push, scatter_cols);
             // more than 8 tokens: tcgen05 / TMEM kernel; 5..8: mma.sync kernel; up to 4: GEMV
             const bool tc = batched && tc_on && nt > 8 && gemm_tc_supported(a.in, a.w_q8);
-            int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl) : (batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl));
+            int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl) : (batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl_in));
             if (rc2) return rc2;
             ++launches;
             linear_ctas += g_linear_last_ctas;
@@ -810,7 +818,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.pos = pos; a.sin_t = c->sin_t; a.cos_t = c->cos_t;
             a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req; a.page_table = page_table;
             a.pt_stride = c->pt_stride;
-            rc = linear(a, r.n_tok, c->x, d.d, c->q, c->qd, true, W.attn_norm);
+            rc = linear(a, r.n_tok, c->x, d.d, c->q, c->qd, true, W.attn_norm, false, 4, 0);
             if (rc) return rc;
         }
         // --- attention over the paged cache
@@ -821,7 +829,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.kv_pool = c->pool; a.geom = c->geom; a.layer = l; a.tok_seq = tok_req; a.tok_pos = pos;
             a.page_table = page_table; a.pt_stride = c->pt_stride; a.n_splits = n_splits; a.tiles_per_split = attn_tps;
             if (n_splits > 1) attn_bind_scratch(a, c->attn_scratch, c->max_tokens);
-            rc = attn_launch(a, dt, s, pdl);
+            rc = attn_launch(a, dt, s, pdl || (!batched && (pdl_edges & 1)));
             if (rc) return rc;
             ++launches;
         }
@@ -832,7 +840,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.in = c->qd; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.res = c->tp_rank == 0 ? c->x : nullptr;
-            rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr, p2p);
+            rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr, p2p, 1, 2);
             if (rc) return rc;
         }
         rc = all_reduce_x();
@@ -843,7 +851,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.w = W.gate_up; a.w_q8 = q8; a.w_scales = w_scales(W.gate_up, (size_t)2 * c->di_l, d.d);
             a.in = d.d; a.out = 2 * c->di_l;
             a.epilogue = EPI_SWIGLU; a.di = c->di_l;
-            rc = linear(a, r.n_tok, c->x, d.d, c->act, c->di_l, true, W.ffn_norm);
+            rc = linear(a, r.n_tok, c->x, d.d, c->act, c->di_l, true, W.ffn_norm, false, 2, 3);
             if (rc) return rc;
         }
         // --- down projection + residual
@@ -853,7 +861,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.in = c->di_l; a.out = d.d;
             a.epilogue = c->tp_rank == 0 ? EPI_RESIDUAL : EPI_STORE;
             a.res = c->tp_rank == 0 ? c->x : nullptr;
-            rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr, p2p);
+            rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr, p2p, 3, l + 1 < d.n_layers ? 4 : 5);
             if (rc) return rc;
         }
         rc = all_reduce_x();
@@ -890,8 +898,9 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             a.x = c->x; a.stride_x = d.d; a.x_rows = out_idx + r0; a.n_tok = nt; a.in = d.d; a.out = d.vocab;
             a.prologue = PRO_RMSNORM; a.norm_w = c->out_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
             a.epilogue = EPI_STORE; a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
-            a.pdl_trigger = pdl_trigger; a.early_prefetch = early_prefetch;
-            rc = gemv_launch(a, dt, s, pdl);
+            const bool head_pdl = pdl || (((pdl_edges >> 5) & 1) && c->tp_size == 1);
+            a.pdl_trigger = pdl_trigger; a.early_prefetch = (head_pdl && early_prefetch == 1) ? 3 : early_prefetch;
+            rc = gemv_launch(a, dt, s, head_pdl);
             if (rc) return rc;
             ++launches;
             r0 += nt;
