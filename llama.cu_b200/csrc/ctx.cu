@@ -791,7 +791,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (push) p2p_make_push(c->p2p, (size_t)t0 * stride_out * eb, &a.push, scatter_cols);
             // more than 8 tokens: tcgen05 / TMEM kernel; 5..8: mma.sync kernel; up to 4: GEMV
             const bool tc = batched && tc_on && nt > 8 && gemm_tc_supported(a.in, a.w_q8);
-            int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl) : (batched ? gemm_skinny_launch(a, dt, s, pdl) : gemv_launch(a, dt, s, pdl_in));
+            int rc2 = tc ? gemm_tc_launch(a, dt, s, pdl_in) : (batched ? gemm_skinny_launch(a, dt, s, pdl_in) : gemv_launch(a, dt, s, pdl_in));
             if (rc2) return rc2;
             ++launches;
             linear_ctas += g_linear_last_ctas;

@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
     __shared__ int s_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (a.pdl_trigger == 0) grid_dep_launch();
     const int g = lane >> 2, t4 = lane & 3;
     const int ksplit = gridDim.y, ks = blockIdx.y;
     const int Kper = a.in / ksplit;

@@ -195,6 +195,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)TC_BM * (N + 1) * 4);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (a.pdl_trigger == 0) grid_dep_launch();
     const int nkb = a.in / TC_BK;  // K blocks of a whole row block
     const bool swiglu = a.epilogue == EPI_SWIGLU;
     const int acc_cols = N < 32 ? 32 : N;      // TMEM columns of one accumulator
@@ -229,31 +230,37 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     const uint32_t tmem = sh->tmem_base;
 
     if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer
-        grid_dep_wait();
-        int it = 0;  // stages issued so far (all tiles)
-        for (int u = u_begin; u < u_end && !sh->abort_flag;) {
-            const int rb = u / nkb, kb0 = u - rb * nkb;
-            const int kb1 = min(nkb, kb0 + (u_end - u));
-            u += kb1 - kb0;
-            const int row_a = swiglu ? rb * 64 : rb * TC_BM;
-            const int row_b = swiglu ? a.di + rb * 64 : rb * TC_BM + 64;
-            for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                const int slot = it % n_stages;
-                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
-                if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
-                    atomicOr(status, 4u);
-                    sh->abort_flag = 1;
-                    break;
-                }
-                const uint32_t bar = tc_smem(&sh->full[slot]);
-                const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+        // ---------------- TMA producer: unit j of this CTA is (row block, K block) = divmod(u_begin + j, nkb)
+        const int n_units = u_end - u_begin;
+        auto issue = [&](int j, bool weights, bool acts) {
+            const int u = u_begin + j, rb = u / nkb, kb = u - rb * nkb;
+            const int slot = j % n_stages;
+            const uint32_t bar = tc_smem(&sh->full[slot]);
+            const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+            const int kx = kb * TC_BK;
+            if (weights) {
                 tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
-                const int kx = kb * TC_BK;
-                tc_tma_2d(dst, &map_w, kx, row_a, bar);
-                tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, row_b, bar);
-                tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
+                tc_tma_2d(dst, &map_w, kx, swiglu ? rb * 64 : rb * TC_BM, bar);
+                tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, swiglu ? a.di + rb * 64 : rb * TC_BM + 64, bar);
             }
+            if (acts) tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
+        };
+        // The weights do not depend on the previous kernel: when this launch was allowed to start early
+        // (programmatic dependent launch) the first ring of weight tiles is already streaming while the predecessor
+        // finishes; the activation tiles of those stages follow once it has.
+        const int first = n_units < n_stages ? n_units : n_stages;
+        for (int j = 0; j < first; ++j) issue(j, true, false);
+        grid_dep_wait();
+        for (int j = 0; j < first; ++j) issue(j, false, true);
+        for (int j = first; j < n_units && !sh->abort_flag; ++j) {
+            const int slot = j % n_stages;
+            const uint32_t parity = (uint32_t)(j / n_stages) & 1u;
+            if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            issue(j, true, true);
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer

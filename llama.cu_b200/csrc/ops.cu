@@ -61,6 +61,7 @@ int op_fast_embedding(uint32_t *tokens, const lcu_kv_pair *pairs, const uint32_t
 template <class T, class Tw>
 __global__ void rms_norm_kernel(T *__restrict__ y, int sy, const T *__restrict__ x, int sx,
                                 const Tw *__restrict__ w, float eps, int d) {
+    grid_dep_launch();  // a GEMM launched with the programmatic attribute may start streaming its weights now
     grid_dep_wait();
     const T *xr = x + (size_t)blockIdx.x * sx;
     T *yr = y + (size_t)blockIdx.x * sy;
