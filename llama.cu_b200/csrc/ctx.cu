@@ -691,7 +691,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     // programmatic dependent launch on selected edges of a layer only (bit 0: QKV -> attention, 1: attention -> O,
     // 2: O -> gate|up, 3: gate|up -> down, 4: down -> next QKV): the successor is launched with the attribute and the
     // predecessor releases it as soon as all its CTAs are running
-    static const int pdl_edges = getenv("LCU_PDL_EDGES") ? atoi(getenv("LCU_PDL_EDGES")) : 28;
+    static const int pdl_edges_env = getenv("LCU_PDL_EDGES") ? atoi(getenv("LCU_PDL_EDGES")) : -1;
     static const int early_prefetch = getenv("LCU_PREFETCH") ? atoi(getenv("LCU_PREFETCH")) : 1;
     int launches = 0;
     unsigned char *D = c->desc_dev;
@@ -737,6 +737,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     int n_splits, attn_tps;
     attn_plan(c, r.n_tok, &n_splits, &attn_tps);
     const bool batched = c->batched_ok && r.n_tok >= batched_min_tokens();
+    // GEMV rounds: the three GEMV -> GEMV edges (the edges around attention lose there); batched rounds: also attention -> O
+    const int pdl_edges = pdl_edges_env >= 0 ? pdl_edges_env : (batched ? 30 : 28);
     gemm_skinny_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096);
     gemm_tc_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096, c->dev_status);
     static const bool tc_on = !(getenv("LCU_TC") && getenv("LCU_TC")[0] == '0');
