@@ -56,6 +56,40 @@ __device__ __forceinline__ void q8x4_to_h2(uint32_t q, uint32_t &h01, uint32_t &
     h23 = *reinterpret_cast<uint32_t *>(&b);
 }
 
+// Fused epilogue of a thread's 2 x NTL (pair, token) values.  The residual is updated in place, so the compiler cannot
+// move the residual loads of one item above the stores of the previous one: they are all fetched first.
+template <class T, int NTL>
+__device__ __forceinline__ void sk_finish(const GemvArgs &a, int pair, int t4, float acc[NTL][4]) {
+    if (a.epilogue == EPI_RESIDUAL && a.push.n == 0) {
+        const size_t r = (size_t)pair * 2;
+        uint32_t res[NTL][2];
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int n = nt * 8 + 2 * t4 + k;
+                res[nt][k] = n < a.n_tok ? *reinterpret_cast<const uint32_t *>(reinterpret_cast<const T *>(a.res) + (size_t)n * a.stride_res + r) : 0u;
+            }
+#pragma unroll
+        for (int nt = 0; nt < NTL; ++nt)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int n = nt * 8 + 2 * t4 + k;
+                if (n >= a.n_tok) continue;
+                const float2 rf = Act<T>::to_f2(res[nt][k]);
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.y) + (size_t)n * a.stride_y + r) =
+                    Act<T>::pack(acc[nt][k] + rf.x, acc[nt][2 + k] + rf.y);
+            }
+        return;
+    }
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+        const int n0 = nt * 8 + 2 * t4;
+        if (n0 < a.n_tok) gemv_epilogue<T>(a, pair, n0, acc[nt][0], acc[nt][2]);
+        if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, acc[nt][1], acc[nt][3]);
+    }
+}
+
 // Q8 = true (f16 activations only): weights are the repacked Q8_0 planes, int8 [out, in] then f16 scales
 // [out, in/32].  Inside a 64-wide K block lane t4 owns k = 8 t4 .. 8 t4 + 7 of EACH 32-wide quantisation block
 // (two 8-byte loads per row), so every pair of MMAs stays inside one quantisation block: its products are summed
@@ -195,14 +229,7 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
 
     if (ksplit == 1) {
         // a thread holds both rows of its pair for tokens 2t and 2t+1 of every token tile
-        if (pv) {
-#pragma unroll
-            for (int nt = 0; nt < NTL; ++nt) {
-                int n0 = nt * 8 + 2 * t4;
-                if (n0 < a.n_tok) gemv_epilogue<T>(a, pair, n0, acc[nt][0], acc[nt][2]);
-                if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, acc[nt][1], acc[nt][3]);
-            }
-        }
+        if (pv) sk_finish<T, NTL>(a, pair, t4, acc);
         p2p_signal(a.push);
         return;
     }
@@ -228,17 +255,27 @@ __global__ void __launch_bounds__(SK_THREADS, (NTL <= 4 ? 2 : 1)) gemm_skinny_ke
     }
     __threadfence();
     if (pv) {
+        // the partial sums of two token tiles at a time are all requested before the first add (one L2 round trip
+        // per two tiles instead of one per split and tile)
 #pragma unroll
-        for (int nt = 0; nt < NTL; ++nt) {
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int j = 0; j < ksplit; ++j) {
-                float4 v = __ldcg(reinterpret_cast<const float4 *>(ws + (((size_t)j * n_pairs + pair) * N + nt * 8 + 2 * t4) * 2));
-                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        for (int nt0 = 0; nt0 < NTL; nt0 += 2) {
+            float4 part[2][8];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < ksplit)
+                        part[i][j] = __ldcg(reinterpret_cast<const float4 *>(ws + (((size_t)j * n_pairs + pair) * N + (nt0 + i) * 8 + 2 * t4) * 2));
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (j < ksplit) { sum.x += part[i][j].x; sum.y += part[i][j].y; sum.z += part[i][j].z; sum.w += part[i][j].w; }
+                acc[nt0 + i][0] = sum.x; acc[nt0 + i][2] = sum.y; acc[nt0 + i][1] = sum.z; acc[nt0 + i][3] = sum.w;
             }
-            int n0 = nt * 8 + 2 * t4;
-            if (n0 < a.n_tok) gemv_epilogue<T>(a, pair, n0, sum.x, sum.y);
-            if (n0 + 1 < a.n_tok) gemv_epilogue<T>(a, pair, n0 + 1, sum.z, sum.w);
         }
+        sk_finish<T, NTL>(a, pair, t4, acc);
     }
     p2p_signal(a.push);
 }
