@@ -90,6 +90,18 @@ template <class T> __device__ __forceinline__ float dot8_mixed(const uint4 &w, c
     return acc;
 }
 
+// int8 x 4 -> two f16x2 without I2F: bytes xor 0x80 land in the mantissa of 1024.0 (0x64xx = 1024 + byte),
+// minus 1152 gives the signed value exactly.
+__device__ __forceinline__ void q8x4_to_h2(uint32_t q, uint32_t &h01, uint32_t &h23) {
+    const uint32_t u = q ^ 0x80808080u;
+    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));
+    uint32_t ua = __byte_perm(u, 0x64646464u, 0x4140), ub = __byte_perm(u, 0x64646464u, 0x4342);
+    __half2 a = __hsub2(*reinterpret_cast<__half2 *>(&ua), bias);
+    __half2 b = __hsub2(*reinterpret_cast<__half2 *>(&ub), bias);
+    h01 = *reinterpret_cast<uint32_t *>(&a);
+    h23 = *reinterpret_cast<uint32_t *>(&b);
+}
+
 // ------------------------------------------------------------------ memory access
 // 128-bit streaming load for data read exactly once per step (weights): no L1 allocation,
 // read-only path.

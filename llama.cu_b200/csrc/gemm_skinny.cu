@@ -44,18 +44,6 @@ __device__ __forceinline__ void sk_cp_async_16(void *smem_dst, const void *gsrc,
 // grid = (row blocks of 64 pairs, K splits).  With more than one K split the partial sums go through
 // `ws` [split][pair][token][2] and the last CTA of a row block to arrive (ticket) adds them in split
 // order and runs the epilogue, so the result does not depend on which CTA finishes last.
-// int8 x 4 -> two f16x2 without I2F: bytes xor 0x80 land in the mantissa of 1024.0 (0x64xx = 1024 + byte),
-// minus 1152 gives the signed value exactly.
-__device__ __forceinline__ void q8x4_to_h2(uint32_t q, uint32_t &h01, uint32_t &h23) {
-    const uint32_t u = q ^ 0x80808080u;
-    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));
-    uint32_t ua = __byte_perm(u, 0x64646464u, 0x4140), ub = __byte_perm(u, 0x64646464u, 0x4342);
-    __half2 a = __hsub2(*reinterpret_cast<__half2 *>(&ua), bias);
-    __half2 b = __hsub2(*reinterpret_cast<__half2 *>(&ub), bias);
-    h01 = *reinterpret_cast<uint32_t *>(&a);
-    h23 = *reinterpret_cast<uint32_t *>(&b);
-}
-
 // Fused epilogue of a thread's 2 x NTL (pair, token) values.  The residual is updated in place, so the compiler cannot
 // move the residual loads of one item above the stores of the previous one: they are all fetched first.
 template <class T, int NTL>

@@ -20,6 +20,8 @@
 //     dependent launch the weights of this GEMV already stream while the previous kernel
 //     of the step drains; only then are the activations staged to shared memory;
 //   - Q8_0 weights (int8 quants + one f16 scale per 32) are dequantised in registers.
+#include <type_traits>
+
 #include "gemv.cuh"
 
 #include <cstdlib>
@@ -197,6 +199,32 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
                     for (int r = 0; r < R; ++r)
 #pragma unroll
                         for (int t = 0; t < NT; ++t) acc[r][t] = dot8_mixed<T>(wreg[r][ki], xv[t], acc[r][t]);
+                } else if constexpr (std::is_same<T, __half>::value) {
+                    // Q8_0 with f16 activations: int8 -> f16 pairs (prmt + one hsub2 per pair, exact), then the same
+                    // mixed-precision FMA as the f16 path: integer x activation products are exact in f32, summed in
+                    // element order, scaled by the block's scale -- the value of scale * q dequantised in f32
+                    uint4 xv[NT][2];
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) {
+                        const uint4 *xp = reinterpret_cast<const uint4 *>(xs + (size_t)t * a.in) + 2 * kv;
+                        xv[t][0] = xp[0];
+                        xv[t][1] = xp[1];
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        uint4 w0, w1;
+                        q8x4_to_h2(wreg[r][ki].x, w0.x, w0.y);
+                        q8x4_to_h2(wreg[r][ki].y, w0.z, w0.w);
+                        q8x4_to_h2(wreg[r][ki].z, w1.x, w1.y);
+                        q8x4_to_h2(wreg[r][ki].w, w1.z, w1.w);
+                        float sc = __half2float(__ushort_as_half(sreg[r][ki]));
+#pragma unroll
+                        for (int t = 0; t < NT; ++t) {
+                            float d = dot8_mixed<T>(w0, xv[t][0], 0.f);
+                            d = dot8_mixed<T>(w1, xv[t][1], d);
+                            acc[r][t] = fmaf(sc, d, acc[r][t]);
+                        }
+                    }
                 } else {
                     float xf[NT][16];
 #pragma unroll
