@@ -322,7 +322,7 @@ static GemvPlan plan_for(int in, bool q8, int nt) {
     int cap = 8 / nt;  // keep 2*RP*NT accumulators <= 16
     if (cap < 1) cap = 1;
     if (rp > cap) rp = cap;
-    if (q8 && rp > 2) rp = 2;
+    { static const int q8_rp = tune_int("LCU_Q8_RP", 4); if (q8 && rp > q8_rp) rp = q8_rp; }
     best.RP = rp;
     return best;
 }
@@ -379,7 +379,7 @@ static int launch_nt(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStr
 #define LCU_GEMV_CASE(KI_, RP_) \
     if (pl.KI == KI_ && pl.RP == RP_) return launch_inst<T, Q8, NT, KI_, RP_>(a, pl, n_pairs, s, pdl, dry);
     if constexpr (Q8) {
-        LCU_GEMV_CASE(1, 2) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
+        LCU_GEMV_CASE(1, 4) LCU_GEMV_CASE(1, 2) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
     } else if constexpr (NT == 1) {
         LCU_GEMV_CASE(1, 4) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
     } else if constexpr (NT == 2) {
