@@ -474,6 +474,181 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
     }
 }
 
+// ------------------------------------------------------------------ cluster split-K form
+// For matrices with fewer row blocks than SMs.  The KS CTAs that share a row block form a thread-block cluster
+// (consecutive blockIdx.x): each accumulates its K range in TMEM, stages the partial tile token-major in its own
+// shared memory, and after a cluster barrier every CTA sums ITS share of the (token, 8 rows) items over all peers'
+// tiles through distributed shared memory (peers in K order, so the result does not depend on timing) and runs the
+// fused epilogue for them.  No scratch in global memory, no fence / ticket / reload chain: the hand-over costs two
+// cluster barriers and one round of DSMEM loads.  A second cluster barrier keeps every tile alive until all peers
+// have read it.  All threads of all CTAs reach both barriers on every path (a timed-out wait only skips work).
+constexpr int TCK_LD = TC_BM + 4;  // floats per token row of the staged tile (16-byte aligned, bank-skewed)
+
+__device__ __forceinline__ uint32_t tc_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void tc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 tc_ld_dsmem4(uint32_t local_saddr, uint32_t cta) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(cta));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+    return v;
+}
+
+template <class T>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                int N, int n_stages, int KS, uint32_t idesc, uint32_t *status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
+    const int stage_bytes = TC_A_BYTES + N * 128;
+    float *stg = reinterpret_cast<float *>(smem + (size_t)n_stages * stage_bytes);  // [N][TCK_LD]
+    TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)N * TCK_LD * 4);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (a.pdl_trigger == 0) grid_dep_launch();
+    const int nkb = a.in / TC_BK;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+    const int ks = (int)tc_cluster_rank();
+    const int rb = (int)blockIdx.x / KS;
+    const int kb0 = (int)((long)ks * nkb / KS), kb1 = (int)((long)(ks + 1) * nkb / KS);
+    const int n_units = kb1 - kb0;
+    const int tm_cols = N < 32 ? 32 : N;
+
+    if (tid == 0) {
+        for (int i = 0; i < n_stages; ++i) {
+            tc_mbar_init(tc_smem(&sh->full[i]), 1);
+            tc_mbar_init(tc_smem(&sh->empty[i]), 1);
+        }
+        tc_mbar_init(tc_smem(&sh->tmem_full[0]), 1);
+        sh->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)), "r"(tm_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = sh->tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer (weights of the first ring before the dependency wait, as in gemm_tc_kernel)
+        auto issue = [&](int j, bool weights, bool acts) {
+            const int slot = j % n_stages;
+            const uint32_t bar = tc_smem(&sh->full[slot]);
+            const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
+            const int kx = (kb0 + j) * TC_BK;
+            if (weights) {
+                tc_mbar_expect_tx(bar, (uint32_t)stage_bytes);
+                tc_tma_2d(dst, &map_w, kx, swiglu ? rb * 64 : rb * TC_BM, bar);
+                tc_tma_2d(dst + TC_A_BYTES / 2, &map_w, kx, swiglu ? a.di + rb * 64 : rb * TC_BM + 64, bar);
+            }
+            if (acts) tc_tma_2d(dst + TC_A_BYTES, &map_x, kx, 0, bar);
+        };
+        const int first = n_units < n_stages ? n_units : n_stages;
+        for (int j = 0; j < first; ++j) issue(j, true, false);
+        grid_dep_wait();
+        for (int j = 0; j < first; ++j) issue(j, false, true);
+        for (int j = first; j < n_units && !sh->abort_flag; ++j) {
+            const int slot = j % n_stages;
+            const uint32_t parity = (uint32_t)(j / n_stages) & 1u;
+            if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            issue(j, true, true);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer
+        for (int j = 0; j < n_units; ++j) {
+            const int slot = j % n_stages;
+            const uint32_t parity = (uint32_t)(j / n_stages) & 1u;
+            if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
+                atomicOr(status, 4u);
+                sh->abort_flag = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TC_A_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)
+                tc_mma_f16(tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (j > 0 || k > 0) ? 1u : 0u);
+            tc_commit(tc_smem(&sh->empty[slot]));
+        }
+        tc_commit(tc_smem(&sh->tmem_full[0]));
+    } else if (warp >= 2) {
+        // ---------------- accumulator -> token-major staging tile
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[0]), 0u, &sh->abort_flag);
+        if (!ok) {
+            atomicOr(status, 4u);
+            sh->abort_flag = 1;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int c0 = 0; c0 < N; c0 += 16) {
+            uint32_t r[16];
+            if (ok) {
+                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) stg[(size_t)(c0 + i) * TCK_LD + row] = ok ? __uint_as_float(r[i]) : 0.f;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    tc_cluster_sync();  // every CTA of the row block has staged its partial tile
+
+    if (warp >= 2) {
+        // ---------------- this CTA's share of the items: chunk c of 8 rows (8 pairs for SwiGLU) with c % KS == ks
+        const int et = tid - 64;
+        const int chunks = swiglu ? 8 : 16;
+        const int mine = (chunks - ks + KS - 1) / KS;  // chunks ks, ks + KS, ...
+        TcPre pre[8];
+        int cnt = 0;
+        for (int idx = et; idx < mine * N; idx += 128, ++cnt) {
+            const int c = ks + (idx % mine) * KS, n = idx / mine;
+            const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+            if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
+        }
+        cnt = 0;
+        for (int idx = et; idx < mine * N; idx += 128, ++cnt) {
+            const int c = ks + (idx % mine) * KS, n = idx / mine;
+            const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+            if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            const uint32_t sv = tc_smem(stg + (size_t)n * TCK_LD + 8 * c);
+            for (int p = 0; p < KS; ++p) {
+                const float4 lo = tc_ld_dsmem4(sv, (uint32_t)p), hi = tc_ld_dsmem4(sv + 16, (uint32_t)p);
+                v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+                v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+                if (swiglu) {
+                    const float4 l2 = tc_ld_dsmem4(sv + 64 * 4, (uint32_t)p), h2 = tc_ld_dsmem4(sv + 64 * 4 + 16, (uint32_t)p);
+                    u[0] += l2.x; u[1] += l2.y; u[2] += l2.z; u[3] += l2.w;
+                    u[4] += h2.x; u[5] += h2.y; u[6] += h2.z; u[7] += h2.w;
+                }
+            }
+            tc_finish<T>(a, n, first, v, u, pre[cnt]);
+        }
+    }
+    tc_cluster_sync();  // nobody leaves while a peer may still read its tile
+    p2p_signal(a.push);  // no-op without tensor parallelism
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tm_cols) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------ tokens-on-M form
 // D[128 token lanes x BN weight rows] += X[128 x 64] . W_tile[BN x 64]^T: the token block (<= 64 real rows, the
 // rest of the 128-row operand is never read back) is the M side and a tile of BN weight rows the N side.  BN is
@@ -748,6 +923,7 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         if (it == done.end()) {
             LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             LCU_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            LCU_CHECK_CUDA(cudaFuncSetAttribute(gemm_tck_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             void *p = nullptr;
             LCU_CHECK_CUDA(cudaGetSymbolAddress(&p, g_tc_fallback_status));
             it = done.emplace(dev, reinterpret_cast<uint32_t *>(p)).first;
@@ -814,6 +990,42 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
     // the activation map has exactly n_tok rows: the rest of the N-row box is out of bounds and zero-filled
     rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
     if (rc) return rc;
+    // ---- few row blocks: the CTAs of a row block form a cluster and merge through distributed shared memory
+    {
+        // 1: where it measured faster than the stream-K split (64-token blocks: 6.23 -> 6.00 ms per 8B batch-64 step;
+        // very few row blocks: 11.2 -> 8.7 ms for one rank's share of the 70B shape; with 16..32 tokens and 32..48 row
+        // blocks the balanced stream-K split wins: 4.75 against 4.95 ms), 2: wherever it applies, 0: never
+        static const int cluster_mode = getenv("LCU_TC_CLUSTER") ? atoi(getenv("LCU_TC_CLUSTER")) : 1;
+        const int n_rb_c = (n_pairs + 63) / 64, nkb_c = a.in / TC_BK;
+        int KS = sms / n_rb_c;
+        if (KS > 8) KS = 8;
+        while (KS > 1 && nkb_c / KS < 4) --KS;
+        const bool cluster_on = cluster_mode == 2 || (cluster_mode == 1 && (N == 64 || n_rb_c * 5 < sms));
+        if (vec && cluster_on && KS >= 2) {
+            const int stage_bytes = TC_A_BYTES + N * 128;
+            const size_t fixed = 1024 + (size_t)N * TCK_LD * 4 + sizeof(TcShared) + 64;
+            int st = (int)(((size_t)227 * 1024 - fixed) / stage_bytes);
+            if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
+            const uint32_t idesc_c = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(n_rb_c * KS);
+            cfg.blockDim = dim3(TC_THREADS);
+            cfg.dynamicSmemBytes = fixed + (size_t)st * stage_bytes;
+            cfg.stream = s;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)KS;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = pdl ? 2 : 1;
+            LCU_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tck_kernel<T>, a, mw, mx, N, st, KS, idesc_c, status));
+            g_linear_last_ctas = n_rb_c * KS;
+            return LCU_OK;
+        }
+    }
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
     // Work split (stream-K): the (row block, K block) units are dealt to the SMs in equal contiguous ranges, so
     // the launch is balanced whatever the row-block count; row blocks cut between CTAs are summed through scratch.
