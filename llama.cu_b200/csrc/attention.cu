@@ -48,6 +48,26 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t r[4], const void *sme
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+// thread-block cluster helpers for the split-KV merge through distributed shared memory
+__device__ __forceinline__ void att_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t att_map_peer(const void *local, uint32_t cta) {
+    uint32_t la = (uint32_t)__cvta_generic_to_shared(local), ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta));
+    return ra;
+}
+__device__ __forceinline__ float att_ld_peer(uint32_t ra) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 att_ld_peer2(uint32_t ra) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(ra) : "memory");
+    return v;
+}
+
 // Both products run on tensor cores (mma.sync m16n8k16, f32 accumulation):
 //   scores  S[pos][head] = K[pos][:] . q[head][:]   M = 16 positions per warp, N = 8 head slots (G used), K = dh
 //   output  O[head][d]   = P[head][:] . V[:][d]     M = 16 head slots (G used), N = dh / 4 per warp, K = 64 positions
@@ -88,7 +108,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     int tps = (n_tiles + a.n_splits - 1) / a.n_splits;
     if (a.tiles_per_split > tps) tps = a.tiles_per_split;
     const int my_splits = (n_tiles + tps - 1) / tps;
-    if (sp >= my_splits) return;
+    // cluster_z > 0: the splits of a (token, KV head) are one thread-block cluster and merge through distributed
+    // shared memory; CTAs without work still take part in its two barriers
+    const bool clus = a.cluster_z > 0;
+    if (sp >= my_splits) {
+        if (clus) {
+            att_cluster_sync();
+            att_cluster_sync();
+        }
+        return;
+    }
     const int tile0 = sp * tps;
     const int tile1 = min(n_tiles, tile0 + tps);
     const float scale = 1.0f / sqrtf((float)DH);
@@ -251,6 +280,49 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     // this thread holds head slot gid, dimensions warp*DW + 8 i + 2 t4 (+1) in acc[i][0..1]
     const int d0 = warp * DW + 2 * t4;
     T *og = reinterpret_cast<T *>(a.o) + (size_t)t * a.stride_o + (size_t)hkv * G * DH;
+    if (clus) {
+        // unnormalised partial into this CTA's shared memory (the K buffer is free now); m_run / l_run are there already
+        float *Os = reinterpret_cast<float *>(Ks);  // [G][DH]
+        if (my_splits > 1 && gid < G) {
+#pragma unroll
+            for (int i = 0; i < NT; ++i) *reinterpret_cast<float2 *>(Os + gid * DH + d0 + 8 * i) = make_float2(acc[i][0], acc[i][1]);
+        }
+        __syncthreads();
+        att_cluster_sync();
+        if (sp == 0 && gid < G) {
+            if (my_splits == 1) {
+                const float inv = 1.f / l_run[gid];
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+                    *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(acc[i][0] * inv, acc[i][1] * inv);
+            } else {
+                float M = -INFINITY;
+                for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, att_ld_peer(att_map_peer(m_run + gid, (uint32_t)s2)));
+                float L = 0.f, O[NT][2];
+#pragma unroll
+                for (int i = 0; i < NT; ++i) O[i][0] = O[i][1] = 0.f;
+                for (int s2 = 0; s2 < my_splits; ++s2) {
+                    const float ms = att_ld_peer(att_map_peer(m_run + gid, (uint32_t)s2));
+                    const float ls = att_ld_peer(att_map_peer(l_run + gid, (uint32_t)s2));
+                    const float w = ms == -INFINITY ? 0.f : expf(ms - M);
+                    L = fmaf(ls, w, L);
+                    const uint32_t ob = att_map_peer(Os + gid * DH + d0, (uint32_t)s2);
+#pragma unroll
+                    for (int i = 0; i < NT; ++i) {
+                        const float2 o = att_ld_peer2(ob + 32 * i);
+                        O[i][0] = fmaf(o.x, w, O[i][0]);
+                        O[i][1] = fmaf(o.y, w, O[i][1]);
+                    }
+                }
+                const float inv = 1.f / L;
+#pragma unroll
+                for (int i = 0; i < NT; ++i)
+                    *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(O[i][0] * inv, O[i][1] * inv);
+            }
+        }
+        att_cluster_sync();  // nobody leaves while the first split may still read its partial
+        return;
+    }
     if (my_splits == 1) {
         if (gid < G) {
             const float inv = 1.f / l_run[gid];
@@ -347,6 +419,25 @@ static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     }
     if (dry) return LCU_OK;
     dim3 grid(a.nkvh, a.n_tok, a.n_splits);
+    if (a.cluster_z > 0) {
+        LCU_REQUIRE(a.cluster_z == a.n_splits && a.cluster_z <= 8, "attention: cluster of %d splits (grid depth %d, at most 8)", a.cluster_z, a.n_splits);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(ATT_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = (unsigned)a.cluster_z;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 2 : 1;
+        LCU_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, a));
+        return LCU_OK;
+    }
     LCU_CHECK_CUDA(launch_kernel(kernel, grid, dim3(ATT_THREADS), smem, s, pdl, a));
     return LCU_OK;
 }
@@ -367,7 +458,7 @@ int attn_launch(const AttnArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
     LCU_REQUIRE(a.nkvh > 0 && a.nh % a.nkvh == 0, "attention: nh = %d is not a multiple of nkvh = %d", a.nh, a.nkvh);
     LCU_REQUIRE(a.dh == 64 || a.dh == 128, "attention: dh = %d unsupported (64, 128)", a.dh);
     LCU_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535 && a.n_tok <= 65535, "attention: grid out of range");
-    LCU_REQUIRE(dry || a.n_splits == 1 || (a.part_o && a.part_ml && a.counters), "attention: split-KV needs scratch");
+    LCU_REQUIRE(dry || a.n_splits == 1 || a.cluster_z > 0 || (a.part_o && a.part_ml && a.counters), "attention: split-KV needs scratch");
     if (!a.kv_pool && !dry) {
         LCU_REQUIRE(a.k_lin && a.v_lin, "attention: no cache given");
         LCU_REQUIRE(a.stk % 8 == 0 && a.shk % 8 == 0 && a.stv % 8 == 0 && a.shv % 8 == 0 &&

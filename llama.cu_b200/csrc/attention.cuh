@@ -26,6 +26,8 @@ struct AttnArgs {
     int n_splits;          // grid depth = most splits any token of the round can need
     int tiles_per_split;   // 64-position tiles one CTA walks (0: context / n_splits); a token with a short
                            // context uses fewer splits and the CTAs beyond them exit at once
+    int cluster_z;         // > 0 (== n_splits, <= 8): the splits form a thread-block cluster and merge through
+                           // distributed shared memory instead of the scratch below
     float *part_o;        // [n_tok, nh, n_splits, dh]
     float *part_ml;       // [n_tok, nh, n_splits, 2]
     unsigned *counters;   // [n_tok, nkvh], zero before the first launch; the kernel re-zeroes them
