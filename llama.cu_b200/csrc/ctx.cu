@@ -756,7 +756,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     static const long scatter_min = getenv("LCU_P2P_SCATTER_MIN") ? atol(getenv("LCU_P2P_SCATTER_MIN")) : 131072;
     // (from 4 ranks on: with 2 ranks both forms move the same bytes and the scatter form only adds a hop —
     // measured 5.5 ms against 4.9 ms per 8B batch-32 step)
-    static const int scatter_ranks = getenv("LCU_P2P_SCATTER_RANKS") ? atoi(getenv("LCU_P2P_SCATTER_RANKS")) : 4;
+    // Off unless asked for (LCU_P2P_SCATTER_RANKS=4 is the intended setting): validated with 2 ranks only so far.
+    static const int scatter_ranks = getenv("LCU_P2P_SCATTER_RANKS") ? atoi(getenv("LCU_P2P_SCATTER_RANKS")) : 99;
     const int scatter_cols = (p2p && c->tp_size >= scatter_ranks && (long)r.n_tok * d.d * 2 >= scatter_min &&
                               d.d % (c->tp_size * 8) == 0) ? d.d / c->tp_size : 0;
     c->p2p.parity = 0;  // every step holds an even number of all-reduces, so captured graphs agree on it
