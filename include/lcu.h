@@ -255,7 +255,12 @@ LCU_API int lcu_op_attention_kv_cached(void *o, int sto, int sho, const void *q,
 LCU_API int lcu_op_all_reduce(lcu_ctx *ctx, void *y, const void *x, size_t count, int dt, lcu_stream_t s);
 
 /* Sampler: drop-in for librandom_sample.so — same names' meaning, argument order and
- * `cudaError_t` return as llama.cu/src/op/random_sample/sample.h:15-39. */
+ * `cudaError_t` return as llama.cu/src/op/random_sample/sample.h:15-39.
+ * One documented difference in `kv_pair.val` of the STOCHASTIC path: the reference's random_sample_kernel
+ * (op/random_sample/sample.cuh:72-87) stores `sorted[i]` after its in-place inclusive scan, i.e. the
+ * unnormalised cumulative weight up to the chosen token; lcu_sample_half and the sampling rows of
+ * lcu_op_sample_rows store the chosen token's logit, as the arg-max path of both libraries does.  The token
+ * index — the only field the token loop consumes (fast_embedding.cuh:7-15, exec/mod.rs:91-115) — is unaffected. */
 LCU_API int lcu_calculate_workspace_size_half(size_t *argmax, size_t *random_sample, size_t n);
 LCU_API int lcu_argmax_half(void *kv_pair, const void *logits, size_t n, void *workspace_ptr, size_t workspace_len,
                     lcu_stream_t stream);

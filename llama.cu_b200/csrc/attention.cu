@@ -5,18 +5,24 @@
 //
 // Arithmetic (the external operator's source is not part of the reference tree, so this
 // is the stated contract rather than a transcription): score = (q·k) / sqrt(dh) in f32,
-// softmax in f32 over positions [0, pos], output = sum p·v in f32, one rounding to the
-// activation dtype.  Query head h reads KV head h / (nh/nkvh).
+// softmax in f32 over positions [0, pos], probabilities rounded to the activation dtype,
+// output = sum p·v in f32, one rounding to the activation dtype.  Query head h reads KV
+// head h / (nh/nkvh).
 //
-// Shape of the kernel: a CTA owns (token, KV head, split) and serves all G = nh/nkvh
-// query heads of that KV head from one pass over the keys/values (GQA packing: KV bytes
-// are read once per group, not once per query head).  KV rows are gathered page by page
-// through the page table into a double-buffered shared-memory tile with 16-byte
-// cp.async copies (rows past the context are zero-filled), scores/softmax/PV run out of
-// shared memory with an online (running max / running sum) softmax.  The context is cut
-// into `n_splits` ranges (flash-decoding); each split leaves an unnormalised partial and
-// its (max, sum) in scratch memory and the last split to arrive — found with an atomic
-// ticket — merges them, so no second launch is needed.
+// Shape of the kernel: a CTA (4 warps) owns (KV head, token, split) and serves all
+// G = nh/nkvh query heads of that KV head from one pass over the keys/values (GQA packing:
+// KV bytes are read once per group, not once per query head).  K/V rows are gathered page
+// by page through the page table into one K and one V shared-memory tile with 16-byte
+// cp.async copies (rows past the context are zero-filled); both products run on tensor
+// cores (mma.sync m16n8k16) with an online (running max / running sum) softmax between
+// them.  The context is cut into splits (flash-decoding); the splits of a (token, KV head)
+// merge either through distributed shared memory inside one thread-block cluster or
+// through scratch memory where the last split to arrive — found with an atomic ticket —
+// sums the partials, so no second launch is needed.
+//
+// Under programmatic dependent launch everything that depends only on the round
+// descriptor (context length, page numbers, cached rows of earlier rounds) is done BEFORE
+// the wait on the predecessor (the QKV projection, which writes q and the new K/V row).
 #include "attention.cuh"
 
 #include <map>
@@ -98,9 +104,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const T *kv_pool = reinterpret_cast<const T *>(a.kv_pool);
     const bool paged = kv_pool != nullptr;
 
-    grid_dep_launch();
-    grid_dep_wait();
-
     const int ctx = paged ? (int)a.tok_pos[t] + 1 : a.pos0 + t + 1;
     const int seq = paged ? a.tok_seq[t] : 0;
     const int n_tiles = (ctx + ATT_TILE - 1) / ATT_TILE;
@@ -116,28 +119,12 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
             att_cluster_sync();
             att_cluster_sync();
         }
-        return;
+        return;  // leaving counts as releasing the dependents
     }
+    if (a.pdl_trigger == 0) grid_dep_launch();
     const int tile0 = sp * tps;
     const int tile1 = min(n_tiles, tile0 + tps);
     const float scale = 1.0f / sqrtf((float)DH);
-
-    // query fragments (B operand of the score product): head slot gid, k = 16 ks + 2 t4 (+8)
-    uint32_t qb[KSTEPS][2];
-    {
-        const T *qg = reinterpret_cast<const T *>(a.q) + (size_t)t * a.stride_q + (size_t)hkv * G * DH + (size_t)gid * DH;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            qb[ks][0] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 2 * t4) : 0u;
-            qb[ks][1] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 8 + 2 * t4) : 0u;
-        }
-        for (int i = tid; i < 16 * PROW / 2; i += ATT_THREADS) reinterpret_cast<uint32_t *>(Ps)[i] = 0u;
-        if (tid < G) {
-            m_run[tid] = -INFINITY;
-            l_run[tid] = 0.f;
-            corr[tid] = 1.f;
-        }
-    }
 
     // Page numbers are fetched into shared memory a window of tiles at a time (128 pages: 32 to 128 tiles),
     // so the gathers below have no dependent global load in front of their copies.
@@ -156,8 +143,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const size_t voff = paged ? (size_t)a.geom.nkvh * blk : 0;
     const int lcol8 = (tid % CH) * 8, j0 = tid / CH;  // this thread's 16-byte column and first row of a tile
 
-    // gathers the K (which = 0) or V (which = 1) rows of a tile; rows past the context are zero-filled
-    auto load_rows = [&](int tile, int which) {
+    // gathers the K (which = 0) or V (which = 1) rows of a tile; rows past the context are zero-filled.
+    // rows: 0 = every row, 1 = all but the token's own row (position ctx - 1), 2 = only that row
+    auto load_rows = [&](int tile, int which, int rows) {
         T *dst = which ? Vs : Ks;
         const int w0 = ((tile - tile0) % WT) * ppt;
 #pragma unroll
@@ -165,6 +153,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
             const int j = j0 + (ATT_THREADS / CH) * i;
             const int pos = tile * ATT_TILE + j;
             const bool valid = pos < ctx;
+            if (rows == 1 && pos == ctx - 1) continue;
+            if (rows == 2 && pos != ctx - 1) continue;
             const T *src;
             if (paged) {
                 const int page = pg[w0 + (j >> a.geom.page_shift)];
@@ -181,27 +171,61 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
         }
     };
     fetch_window(tile0);
+    for (int i = tid; i < 16 * PROW / 2; i += ATT_THREADS) reinterpret_cast<uint32_t *>(Ps)[i] = 0u;
+    if (tid < G) {
+        m_run[tid] = -INFINITY;
+        l_run[tid] = 0.f;
+        corr[tid] = 1.f;
+    }
     __syncthreads();
+
+    // One K and one V buffer per CTA, software-pipelined with two cp.async groups per tile: V(t) lands while
+    // the scores and the softmax of tile t run, K(t+1) while the softmax and P.V of tile t run.  Several CTAs
+    // share an SM (shared memory allows 5), which hides what is left.
+    const bool early = paged && a.early_kv;
+    if (early) {  // rows of earlier rounds: in flight while the predecessor drains
+        load_rows(tile0, 0, 1);
+        cp_async_commit();
+        load_rows(tile0, 1, 1);
+        cp_async_commit();
+    }
+    grid_dep_wait();
+
+    // query fragments (B operand of the score product): head slot gid, k = 16 ks + 2 t4 (+8)
+    uint32_t qb[KSTEPS][2];
+    {
+        const T *qg = reinterpret_cast<const T *>(a.q) + (size_t)t * a.stride_q + (size_t)hkv * G * DH + (size_t)gid * DH;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qb[ks][0] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 2 * t4) : 0u;
+            qb[ks][1] = gid < G ? *reinterpret_cast<const uint32_t *>(qg + ks * 16 + 8 + 2 * t4) : 0u;
+        }
+    }
+    if (early) {  // the row the predecessor has just written (if this split holds it)
+        load_rows(tile0, 0, 2);
+        load_rows(tile0, 1, 2);
+        cp_async_commit();
+    } else {
+        load_rows(tile0, 0, 0);
+        cp_async_commit();
+        load_rows(tile0, 1, 0);
+        cp_async_commit();
+    }
 
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
     const int lrow = lane & 15, lcol = (lane >> 4) * 8;  // ldmatrix.x4 address pattern of this lane
 
-    // One K and one V buffer per CTA, software-pipelined with two cp.async groups per tile: V(t) lands while
-    // the scores and the softmax of tile t run, K(t+1) while the softmax and P.V of tile t run.  Several CTAs
-    // share an SM (shared memory allows 5), which hides what is left.
-    load_rows(tile0, 0);
-    cp_async_commit();
-    load_rows(tile0, 1);
-    cp_async_commit();
     for (int tile = tile0; tile < tile1; ++tile) {
         if (paged && tile + 1 < tile1 && (tile + 1 - tile0) % WT == 0) {
             __syncthreads();  // every copy that reads the old window has been issued
             fetch_window(tile + 1);
         }
-        cp_async_wait<1>();  // K(tile) has landed; V(tile) may still be in flight
+        if (early && tile == tile0) cp_async_wait<0>();  // old rows and the new row of K and V
+        else cp_async_wait<1>();                         // K(tile) has landed; V(tile) may still be in flight
         __syncthreads();
+        if (a.pdl_trigger == 1 && tile == tile0) grid_dep_launch();
 
         // scores of positions [16 warp, 16 warp + 16) for every head slot
         {
@@ -224,7 +248,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
             }
         }
         __syncthreads();  // scores complete, K buffer free
-        if (tile + 1 < tile1) load_rows(tile + 1, 0);
+        if (tile + 1 < tile1) load_rows(tile + 1, 0, 0);
         cp_async_commit();
 
         // online softmax, one warp per head
@@ -272,7 +296,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
             }
         }
         __syncthreads();  // V buffer and probabilities free
-        if (tile + 1 < tile1) load_rows(tile + 1, 1);
+        if (tile + 1 < tile1) load_rows(tile + 1, 1, 0);
         cp_async_commit();
     }
     cp_async_wait<0>();

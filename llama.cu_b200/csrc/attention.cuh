@@ -28,6 +28,12 @@ struct AttnArgs {
                            // context uses fewer splits and the CTAs beyond them exit at once
     int cluster_z;         // > 0 (== n_splits, <= 8): the splits form a thread-block cluster and merge through
                            // distributed shared memory instead of the scratch below
+    // Programmatic dependent launch.  early_kv: the round holds ONE new token per sequence, so every cached row below
+    // a token's own position was written by an earlier round and may be fetched before the wait on the predecessor
+    // (which writes only the new row).  pdl_trigger: 0 = dependents may start as soon as this grid is resident,
+    // 1 = once a CTA's first K/V tile has landed (its remaining traffic is on chip).
+    int early_kv;
+    int pdl_trigger;
     float *part_o;        // [n_tok, nh, n_splits, dh]
     float *part_ml;       // [n_tok, nh, n_splits, 2]
     unsigned *counters;   // [n_tok, nkvh], zero before the first launch; the kernel re-zeroes them

@@ -683,6 +683,7 @@ int mk_build_phases(lcu_ctx *c) {
 struct Round {
     int n_tok, n_req, n_fast;
     bool any_sampling;
+    bool decode_only;  // one new token per sequence
     DescLayout L;
 };
 
@@ -690,8 +691,8 @@ struct Round {
 int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t s, int *count) {
     const lcu_model_desc &d = c->desc;
     const int dt = c->dt;
-    // Programmatic dependent launch measured slower than plain graph edges for this chain of
-    // short kernels on B200 (3.8 ms vs 3.3 ms per 8B step), so it is off unless LCU_PDL=1.
+    // Programmatic dependent launch is used edge by edge (pdl_edges below); putting the attribute on EVERY launch
+    // measured slower than plain graph edges (3.8 ms vs 3.3 ms per 8B step) and stays off unless LCU_PDL=1.
     static const bool pdl = getenv("LCU_PDL") && getenv("LCU_PDL")[0] == '1';
     static const int pdl_trigger = getenv("LCU_PDL_TRIGGER") ? atoi(getenv("LCU_PDL_TRIGGER")) : 2;
     // programmatic dependent launch on selected edges of a layer only (bit 0: QKV -> attention, 1: attention -> O,
@@ -843,6 +844,11 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             // scratch merge (many CTAs without work would sit in cluster barriers: 4.77 -> 5.75 ms at batch 32).
             static const int attn_cluster = getenv("LCU_ATTN_CLUSTER") ? atoi(getenv("LCU_ATTN_CLUSTER")) : 1;
             a.cluster_z = (attn_cluster && !batched && n_splits >= 2 && n_splits <= 8) ? n_splits : 0;
+            // decode rounds: cached rows of earlier rounds are fetched before the wait on the QKV projection
+            static const int attn_early = getenv("LCU_ATTN_EARLY") ? atoi(getenv("LCU_ATTN_EARLY")) : 1;
+            static const int attn_trigger = getenv("LCU_ATTN_TRIGGER") ? atoi(getenv("LCU_ATTN_TRIGGER")) : 1;
+            a.early_kv = (attn_early && r.decode_only) ? 1 : 0;
+            a.pdl_trigger = attn_trigger;
             rc = attn_launch(a, dt, s, pdl || (!batched && (pdl_edges & 1)));
             if (rc) return rc;
             ++launches;
@@ -1094,7 +1100,7 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
 
     // stage the round descriptor in the next pinned buffer (BufN, exec/engine.rs:373-429)
     Round r;
-    r.n_tok = n_tok; r.n_req = n_req; r.n_fast = n_fast; r.any_sampling = any_sampling;
+    r.n_tok = n_tok; r.n_req = n_req; r.n_fast = n_fast; r.any_sampling = any_sampling; r.decode_only = decode_only;
     r.L = desc_layout(n_tok, n_req, c->pt_stride);
     cudaStream_t s = as_stream(stream);
     int slot = c->ring_idx;

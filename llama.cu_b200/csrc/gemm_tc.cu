@@ -326,11 +326,15 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            // the barrier also ANDs every thread's `ok`: the 128 epilogue threads leave the loop together or not at
+            // all (a thread whose wait ran out must not strand the others at the next barrier)
+            uint32_t all_ok;
+            asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.and.pred q, 2, 128, p;\n selp.u32 %0, 1, 0, q;\n}"
+                         : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
             if (et == 0) {  // the accumulator may be overwritten from here on
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&sh->tmem_empty[ab])) : "memory");
             }
-            if (!ok) break;
+            if (!all_ok) break;
             const int items = 64 * N;
             if (whole && vec) {
                 // (token, 8 outputs) items; residual vectors are fetched first, then everything is stored
@@ -393,7 +397,7 @@ gemm_tc_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, cons
                     // it and one dependent round trip costs more than a microsecond here, so the loads of up to 6
                     // segments for TWO rows of 8 floats are all issued before the first add (96 registers of loads in
                     // flight per thread; the epilogue warps have registers to spare), the adds then run in K order.
-                    // Measured: 11 us -> see the profile for a 6-segment merge of a 128 x 32 tile.
+                    // Measured on a 6-segment merge of a 128 x 32 tile: 11 us with one segment after the other.
                     const size_t seg_stride = (size_t)N * TC_BM;
                     auto merge2 = [&](const float *r0, const float *r1, float o0[8], float o1[8]) {
                         float4 b0[12], b1[12];
@@ -820,11 +824,15 @@ gemm_tcn_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, con
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            // the barrier also ANDs every thread's `ok`: the 128 epilogue threads leave the loop together or not at
+            // all (a thread whose wait ran out must not strand the others at the next barrier)
+            uint32_t all_ok;
+            asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.and.pred q, 2, 128, p;\n selp.u32 %0, 1, 0, q;\n}"
+                         : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
             if (et == 0) {  // the accumulator may be overwritten from here on
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&sh->tmem_empty[ab])) : "memory");
             }
-            if (!ok) break;
+            if (!all_ok) break;
         }
     }
     // ---------------- tail

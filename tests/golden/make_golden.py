@@ -27,6 +27,8 @@ CASES = {
     "tiny_batch": ("tiny", None, [5, 16, 33], 8, 0, 2),
     "llama1b_L1": ("llama1b", (1, 2048), [12], 4, 3, 4),
     "llama8b_q8_L1": ("llama8b_q8", (1, 1024), [9], 3, 5, 6),
+    # the reduced shape bench.py checks its tensor-parallel transports on before timing (8 KV heads: TP 2/4/8)
+    "llama8b_L2_tp": ("llama8b", (2, 2048), [5, 9, 40], 8, 7, 8),
 }
 
 

@@ -28,3 +28,89 @@ def greedy_parity(gpu_ids, orc_ids, orc_logits, tol):
             lg = np.sort(orc_logits[i])
             return i, float(lg[-1] - lg[-2])
     return len(orc_ids), None
+
+
+class _LazyHostWeights:
+    """dict-like view over device weights whose .items() yields host copies one tensor at a time,
+    so that a full-size model never has a second complete host copy beside the oracle's f32 one."""
+
+    def __init__(self, dev_weights, cfg):
+        self.dev, self.cfg = dev_weights, cfg
+
+    def items(self):
+        for key, t in self.dev.items():
+            yield key, host_weight(self.cfg, key[1], t)
+
+
+def host_weight(cfg, kind, t):
+    """Host form of one device weight as the oracle takes it: uint16 bit patterns, or for a Q8_0
+    linear weight (plane layout on the device) the dict with the ggml 34-byte blocks."""
+    from llama_cu_b200 import LINEAR_KINDS, Q8_0
+    if cfg.wdt == Q8_0 and kind in LINEAR_KINDS:
+        rows, cols = cfg.shapes()[kind]
+        n = rows * cols
+        q = t[:n].view(torch.int8).view(-1, 32)
+        sc = t[n:].view(-1, 2)
+        blocks = torch.cat([sc, q.view(torch.uint8)], dim=1).reshape(-1).cpu().numpy()
+        return {"q": q.view(rows, cols).cpu().numpy(), "scales": sc.reshape(-1).cpu().numpy().view(np.float16).reshape(rows, cols // 32),
+                "blocks": blocks}
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def device_weights(L, cfg, seed=0, device="cuda:0"):
+    """Seeded synthetic weights drawn on the GPU (seconds even for the 8B shape, where the numpy
+    generator needs minutes).  Returns (device dict for load_model, lazy host view for the oracle)."""
+    dev = L.synth_weights_torch(cfg, seed, device)
+    return dev, _LazyHostWeights(dev, cfg)
+
+
+def teacher_forced_decode(ctx, prompts, o_ids, steps, stream=None):
+    """Prefills every prompt alone, then decodes all sequences together for steps-1 rounds feeding the
+    ORACLE's ids.  Returns (logits [n][steps][vocab] f32, ids the GPU picked [n][steps])."""
+    n = len(prompts)
+    dev = f"cuda:{ctx.device}"
+    out = torch.zeros(max(n, 1), 2, dtype=torch.int32, device=dev)
+    seqs = [ctx.seq_create() for _ in prompts]
+    lgs = [[] for _ in prompts]
+    ids = [[] for _ in prompts]
+
+    def sync():
+        if stream is not None:
+            stream.synchronize()
+        torch.cuda.synchronize(ctx.device)
+
+    for i, p in enumerate(prompts):
+        ctx.step([(seqs[i], 0, len(p))], p, out, stream=stream)
+        sync()
+        lgs[i].append(ctx.logits(1)[0].float().cpu().numpy())
+        ids[i].append(int(out[0, 0].item()))
+    pos = [len(p) for p in prompts]
+    for s in range(steps - 1):
+        reqs = [(seqs[i], pos[i], 1) for i in range(n)]
+        ctx.step(reqs, np.array([o_ids[i][s] for i in range(n)], np.uint32), out, stream=stream)
+        sync()
+        lg = ctx.logits(n).float().cpu().numpy()
+        got = out[:n, 0].cpu().numpy().view(np.uint32)
+        for i in range(n):
+            lgs[i].append(lg[i])
+            ids[i].append(int(got[i]))
+            pos[i] += 1
+    for s in seqs:
+        ctx.seq_free(s)
+    return lgs, ids
+
+
+def parity_report(g_lgs, g_ids, o_lgs, o_ids, tol):
+    """Teacher-forced comparison.  Returns (worst |logit difference|, steps whose arg-max equals the
+    oracle's, all steps, list of (seq, step, oracle margin) where it does not)."""
+    worst, exact, total, off = 0.0, 0, 0, []
+    for i in range(len(o_ids)):
+        for s in range(len(o_ids[i])):
+            worst = max(worst, float(np.abs(g_lgs[i][s] - o_lgs[i][s]).max()))
+            total += 1
+            if g_ids[i][s] == o_ids[i][s]:
+                exact += 1
+            else:
+                lg = np.sort(o_lgs[i][s])
+                off.append((i, s, float(lg[-1] - lg[-2])))
+    return worst, exact, total, off

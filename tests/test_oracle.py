@@ -22,7 +22,7 @@ def _case_cfg(L, case):
     return cfg
 
 
-@pytest.mark.parametrize("name", ["tiny", "tiny_batch", "llama1b_L1", "llama8b_q8_L1"])
+@pytest.mark.parametrize("name", ["tiny", "tiny_batch", "llama1b_L1", "llama8b_q8_L1", "llama8b_L2_tp"])
 def test_oracle_matches_golden(L, O, name):
     case = json.load(open(GOLDEN))[name]
     cfg = _case_cfg(L, case)

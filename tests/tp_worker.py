@@ -1,10 +1,15 @@
 """One rank of the tensor-parallel parity check; run under torchrun by test_tp_gpu.py:
 
-    python -m torch.distributed.run --nproc-per-node N tests/tp_worker.py <config> <layers> <vocab> <steps> <out.json> [p2p]
+    python -m torch.distributed.run --nproc-per-node N tests/tp_worker.py <spec.json> <out.npz> [nccl|p2p]
 
-Every rank loads its slice of the same seeded weights, all ranks run the same rounds, rank 0
-writes the greedy ids and the last round's logits.  With `p2p` the all-reduces and the token
-broadcast go over NVLink peer memory instead of NCCL."""
+spec.json: {"name", "layers", "vocab", "steps", "lengths": [...], "ids": [[...]]} where `ids` are the
+ORACLE's greedy ids.  Every rank loads its slice of the same seeded weights and all ranks run the same
+rounds.  Phase 1 is teacher-forced (the oracle's ids go in on every rank) and rank 0 keeps the logits of
+EVERY step; phase 2 repeats the run free-running with the sampled ids fed back on the device, which under
+tensor parallelism also exercises the token broadcast from the lead rank.  With `p2p` the all-reduces and
+the broadcast go over NVLink peer memory instead of NCCL.  Rank 0 writes logits, ids and the device status
+word of every rank.
+"""
 import ctypes as C
 import json
 import os
@@ -20,16 +25,7 @@ import llama_cu_b200 as L  # noqa: E402
 from llama_cu_b200.model import reduced  # noqa: E402
 
 
-def main():
-    name, layers, vocab, steps, out_path = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5]
-    use_p2p = len(sys.argv) > 6 and sys.argv[6] == "p2p"
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dev = f"cuda:{local}"
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    dist.init_process_group("nccl", device_id=torch.device(dev))
-    lib = L.load_library()
+def make_comm(lib, rank, world, dev):
     uid = torch.zeros(128, dtype=torch.uint8)
     if rank == 0:
         L.check(lib.lcu_comm_unique_id(uid.numpy().ctypes.data))
@@ -38,12 +34,30 @@ def main():
     uid = uid.cpu().contiguous()
     comm = C.c_void_p()
     L.check(lib.lcu_comm_init_rank(uid.numpy().ctypes.data, rank, world, C.byref(comm)))
+    return comm
 
-    cfg = reduced(L.CONFIGS[name], layers, vocab)
+
+def main():
+    spec = json.load(open(sys.argv[1]))
+    out_path = sys.argv[2]
+    use_p2p = len(sys.argv) > 3 and sys.argv[3] == "p2p"
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=torch.device(dev))
+    lib = L.load_library()
+    comm = make_comm(lib, rank, world, dev)
+
+    cfg = reduced(L.CONFIGS[spec["name"]], spec["layers"], spec["vocab"])
+    steps = spec["steps"]
     w = L.synth_weights_numpy(cfg, 0)
     rng = np.random.default_rng(1)
-    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in (5, 9, 40)]
-    ctx = L.load_model(cfg, w, device=local, tp_rank=rank, tp_size=world, comm=comm)
+    prompts = [rng.integers(3, cfg.vocab, n).astype(np.uint32) for n in spec["lengths"]]
+    o_ids = spec["ids"]
+    n = len(prompts)
+    ctx = L.load_model(cfg, w, device=local, tp_rank=rank, tp_size=world, comm=comm, max_seqs=max(n, 1))
     if use_p2p and world > 1:
         def gather(b):
             got = [None] * world
@@ -52,38 +66,64 @@ def main():
         ctx.p2p_connect(gather)
         assert ctx.p2p_enabled
     stream = torch.cuda.Stream(device=dev)
-    n = len(prompts)
     out = torch.zeros(n, 2, dtype=torch.int32, device=dev)
-    seqs = [ctx.seq_create() for _ in prompts]
-    ids = [[] for _ in prompts]
+    logits = np.zeros((n, steps, cfg.vocab), np.float32)
+    tf_ids = np.zeros((n, steps), np.int64)
+    free_ids = np.zeros((n, steps), np.int64)
+
     with torch.cuda.stream(stream):
+        # ---- phase 1: teacher-forced, logits of every step
+        seqs = [ctx.seq_create() for _ in prompts]
+        for i, p in enumerate(prompts):
+            ctx.step([(seqs[i], 0, len(p))], p, out, stream=stream)
+            stream.synchronize()
+            if rank == 0:
+                logits[i, 0] = ctx.logits(1)[0].float().cpu().numpy()
+                tf_ids[i, 0] = int(out[0, 0].item())
+        pos = [len(p) for p in prompts]
+        for s in range(steps - 1):
+            reqs = [(seqs[i], pos[i], 1) for i in range(n)]
+            ctx.step(reqs, np.array([o_ids[i][s] for i in range(n)], np.uint32), out, stream=stream)
+            stream.synchronize()
+            if rank == 0:
+                logits[:, s + 1] = ctx.logits(n).float().cpu().numpy()
+                tf_ids[:, s + 1] = out[:n, 0].cpu().numpy().view(np.uint32)
+            for i in range(n):
+                pos[i] += 1
+        for sq in seqs:
+            ctx.seq_free(sq)
+
+        # ---- phase 2: free-running with device-side feedback (fast_map) and the token broadcast
+        seqs = [ctx.seq_create() for _ in prompts]
+        first = []
         for i, p in enumerate(prompts):
             ctx.step([(seqs[i], 0, len(p))], p, out, stream=stream)
             stream.synchronize()
             t = out[0, :1].clone().to(torch.int64)
             dist.broadcast(t, 0)
-            ids[i].append(int(t.item()))
+            first.append(int(t.item()))
+        free_ids[:, 0] = first
         pos = [len(p) for p in prompts]
         fm = np.array([[i, i] for i in range(n)], np.uint32)
         keep = []
         for s in range(steps - 1):
             reqs = [(seqs[i], pos[i], 1) for i in range(n)]
-            toks = np.array([ids[i][0] for i in range(n)], np.uint32) if s == 0 else np.zeros(n, np.uint32)
+            toks = np.array(first, np.uint32) if s == 0 else np.zeros(n, np.uint32)
             ctx.step(reqs, toks, out, fast_map=None if s == 0 else fm, stream=stream)
             keep.append(out.clone())
             for i in range(n):
                 pos[i] += 1
         stream.synchronize()
     torch.cuda.synchronize()
+    launches = ctx.last_launch_count
+    status = torch.tensor([ctx.device_status()], dtype=torch.int64, device=dev)
+    all_status = [torch.zeros_like(status) for _ in range(world)]
+    dist.all_gather(all_status, status)
     if rank == 0:
-        for o in keep:
-            h = o.cpu().numpy().view(np.uint32)
-            for i in range(n):
-                ids[i].append(int(h[i, 0]))
-        lg = ctx.logits(n).float().cpu().numpy()
-        json.dump({"ids": ids, "logits_last": lg.tolist(), "launches": ctx.last_launch_count,
-                   "status": ctx.device_status(), "p2p": ctx.p2p_enabled}, open(out_path, "w"))
-    assert ctx.device_status() == 0, f"rank {rank}: device status {ctx.device_status()}"
+        for s, o in enumerate(keep):
+            free_ids[:, s + 1] = o[:n, 0].cpu().numpy().view(np.uint32)
+        np.savez(out_path, logits=logits, tf_ids=tf_ids, free_ids=free_ids, launches=launches,
+                 status=np.array([int(t.item()) for t in all_status]), p2p=int(ctx.p2p_enabled))
     dist.barrier()
     ctx.close()
     L.check(lib.lcu_comm_destroy(comm))
