@@ -39,14 +39,6 @@ __device__ __forceinline__ void q8x4_to_f32(uint32_t q, float f[4]) {
     f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.f;
 }
 
-// Named hardware barriers (ids 1..15) shared by `count` threads: arrive does not wait.
-__device__ __forceinline__ void bar_sync_named(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void bar_arrive_named(int id, int count) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 template <class T>
 __device__ __forceinline__ void vec8_to_f32(const uint4 &v, float f[8]) {
     float2 a = Act<T>::to_f2(v.x), b = Act<T>::to_f2(v.y), c = Act<T>::to_f2(v.z), d = Act<T>::to_f2(v.w);
@@ -188,17 +180,6 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
     }
 
     // ---- main loop over row groups
-    // The KS warps that share a row group leave their partial sums in shared memory and ONE of them (ks == 0) adds
-    // them up and runs the epilogue.  The others do not wait for it: they arrive on a named barrier and go on to the
-    // next group (whose weights are already in their registers), at most two groups ahead — the partial buffer has
-    // two halves, and a half is rewritten only after the reducing warp has released it through a second barrier.
-    // The reducing warp requests what its epilogue reads from global memory (residual, sin / cos) before it waits.
-    // With more than three row sub-groups there are not enough hardware barriers and the CTA-wide barrier is used.
-    const int mode = KS == 1 ? 0 : (RS <= 3 && a.sync_mode != 2 ? 1 : 2);  // 0 warp-local, 1 named barriers, 2 __syncthreads
-    const int nthr_k = KS * 32;
-    const bool reducer = ks == 0 && rs < RS && lane < RP * NT;
-    const int my_rp = lane / NT, my_t = lane - my_rp * NT;
-    const EpiTok etok = (reducer && my_t < a.n_tok) ? gemv_epilogue_tok(a, my_t) : EpiTok{0u, 0};
     for (int g = 0; g < n_groups; ++g) {
         float acc[R][NT];
 #pragma unroll
@@ -274,15 +255,7 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
         // next group's weights go in flight before this group is reduced
         if (g + 1 < n_groups) load_group(g + 1);
 
-        const int b = g & 1;
-        const int my_p = p_begin + g * group_pairs + rs * RP + my_rp;
-        const bool emit = reducer && my_p < p_end && my_t < a.n_tok;
-        EpiPre epre{0u, 0.f, 1.f};
-        if (emit) epre = gemv_epilogue_pre<T>(a, my_p, my_t, etok);
-
-        float *pbuf = part + (size_t)b * nwarps * (R * NT);
-        const bool k_reducer = ks == 0;
-        if (mode == 1 && !k_reducer && g >= 2) bar_sync_named(5 + rs * 4 + b, nthr_k);  // half b released
+        float *pbuf = part + (size_t)(g & 1) * nwarps * (R * NT);
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -290,32 +263,19 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
                 float v = warp_sum(acc[r][t]);
                 if (lane == 0) pbuf[warp * (R * NT) + r * NT + t] = v;
             }
-        if (mode == 2) {
-            __syncthreads();
-        } else if (mode == 1) {
-            if (rs < RS) {
-                if (k_reducer) {
-                    bar_sync_named(3 + rs * 4 + b, nthr_k);
-                } else {
-                    __threadfence_block();
-                    bar_arrive_named(3 + rs * 4 + b, nthr_k);
+        __syncthreads();
+        if (ks == 0 && rs < RS && lane < RP * NT) {
+            int rp = lane / NT, t = lane - rp * NT;
+            int p = p_begin + g * group_pairs + rs * RP + rp;
+            if (p < p_end && t < a.n_tok) {
+                float va = 0.f, vb = 0.f;
+                for (int k = 0; k < KS; ++k) {
+                    const float *src = pbuf + (size_t)(rs * KS + k) * (R * NT);
+                    va += src[(2 * rp) * NT + t];
+                    vb += src[(2 * rp + 1) * NT + t];
                 }
+                gemv_epilogue<T>(a, p, t, va, vb);
             }
-        } else {
-            __syncwarp();
-        }
-        if (emit) {
-            float va = 0.f, vb = 0.f;
-            for (int k = 0; k < KS; ++k) {
-                const float *src = pbuf + (size_t)(rs * KS + k) * (R * NT);
-                va += src[(2 * my_rp) * NT + my_t];
-                vb += src[(2 * my_rp + 1) * NT + my_t];
-            }
-            gemv_epilogue<T>(a, my_p, my_t, va, vb, etok, epre);
-        }
-        if (mode == 1 && k_reducer && rs < RS && g + 2 < n_groups) {
-            __syncwarp();
-            bar_arrive_named(5 + rs * 4 + b, nthr_k);  // half b may be rewritten
         }
     }
     if (a.pdl_trigger == 1) grid_dep_launch();
@@ -433,10 +393,7 @@ static int launch_nt(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStr
 }
 
 template <class T, bool Q8>
-static int launch_t(const GemvArgs &a_in, cudaStream_t s, bool pdl, bool dry) {
-    GemvArgs a = a_in;
-    static const int sync_env = tune_int("LCU_GEMV_SYNC", -1);
-    if (sync_env >= 0) a.sync_mode = sync_env;
+static int launch_t(const GemvArgs &a, cudaStream_t s, bool pdl, bool dry) {
     int nt = a.n_tok <= 1 ? 1 : (a.n_tok == 2 ? 2 : 4);
     GemvPlan pl = plan_for(a.in, Q8, nt);
     int n_pairs = a.out / 2;

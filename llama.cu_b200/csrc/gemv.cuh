@@ -46,7 +46,6 @@ struct GemvArgs {
     // tuning: 0 = trigger dependents at kernel start, 1 = after the main loop, 2 = never (implicit at exit)
     int pdl_trigger;
     int early_prefetch;  // 1 = first weight loads before griddepcontrol.wait
-    int sync_mode;       // 0 = asynchronous reduction over named barriers where possible, 2 = CTA-wide barrier per row group
     // tensor parallelism: EPI_STORE / EPI_RESIDUAL outputs go to every rank's all-reduce slot instead of y
     P2pPush push;
 };
@@ -57,62 +56,33 @@ __device__ __forceinline__ float swiglu_act(float gate, float up) {
     return gate * __fdividef(1.f, 1.f + expf(-gate)) * up;
 }
 
-// What the epilogue of one (row pair, token) reads from global memory, split from the arithmetic so that a kernel
-// can issue these loads BEFORE it waits for the accumulated sums (they would otherwise form a chain of dependent
-// round trips at the tail of every row group): per-token constants of the RoPE + KV-append epilogue ...
-struct EpiTok {
-    uint32_t pos;  // position of the token
-    int page;      // KV page holding that position
-};
-// ... and the values that depend on the row pair: the residual pair, or the rotation's sin / cos.
-struct EpiPre {
-    uint32_t res_bits;
-    float sn, cs;
-};
-
-__device__ __forceinline__ EpiTok gemv_epilogue_tok(const GemvArgs &a, int t) {
-    EpiTok k{0u, 0};
-    if (a.epilogue == EPI_ROPE_KV) {
-        k.pos = a.pos[t];
-        k.page = a.page_table[(size_t)a.tok_seq[t] * a.pt_stride + (k.pos >> a.geom.page_shift)];
-    }
-    return k;
-}
-
 template <class T>
-__device__ __forceinline__ EpiPre gemv_epilogue_pre(const GemvArgs &a, int pair, int t, const EpiTok &tok) {
-    EpiPre e{0u, 0.f, 1.f};
-    if (a.epilogue == EPI_RESIDUAL) {
-        const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + (size_t)pair * 2;
-        e.res_bits = *reinterpret_cast<const uint32_t *>(res);
-    } else if (a.epilogue == EPI_ROPE_KV) {
-        const int r = pair * 2;
-        if (r < a.qd + a.kvd) {
-            const int rr = r < a.qd ? r : r - a.qd;
-            const int el = rr % a.dh, half_dh = a.dh >> 1;
-            e.sn = a.sin_t[(size_t)tok.pos * half_dh + (el >> 1)];
-            e.cs = a.cos_t[(size_t)tok.pos * half_dh + (el >> 1)];
-        }
-    }
-    return e;
-}
-
-template <class T>
-__device__ __forceinline__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb, const EpiTok &tok,
-                                              const EpiPre &pre) {
+__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
     T *y = reinterpret_cast<T *>(a.y);
     switch (a.epilogue) {
-    case EPI_STORE:
-    case EPI_RESIDUAL: {
-        const size_t r = (size_t)pair * 2;
-        uint32_t packed;
-        if (a.epilogue == EPI_RESIDUAL) {
-            // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
-            const float2 rf = Act<T>::to_f2(pre.res_bits);
-            packed = Act<T>::pack(va + rf.x, vb + rf.y);
-        } else {
-            packed = Act<T>::pack(va, vb);
+    case EPI_STORE: {
+        size_t r = (size_t)pair * 2;
+        if (a.push.n) {
+            const uint32_t packed = Act<T>::pack(va, vb);
+            if (a.push.scatter_cols) {
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[r / a.push.scatter_cols]) + (size_t)t * a.stride_y + r) = packed;
+                break;
+            }
+            for (int k = 0; k < a.push.n; ++k)
+                *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[k]) + (size_t)t * a.stride_y + r) = packed;
+            break;
         }
+        y[(size_t)t * a.stride_y + r] = Act<T>::from_f(va);
+        y[(size_t)t * a.stride_y + r + 1] = Act<T>::from_f(vb);
+        break;
+    }
+    case EPI_RESIDUAL: {
+        size_t r = (size_t)pair * 2;
+        const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + r;
+        // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
+        uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
+        float2 rf = Act<T>::to_f2(rr);
+        const uint32_t packed = Act<T>::pack(va + rf.x, vb + rf.y);
         if (a.push.n) {
             if (a.push.scatter_cols) {
                 *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.push.slot[r / a.push.scatter_cols]) + (size_t)t * a.stride_y + r) = packed;
@@ -126,42 +96,39 @@ __device__ __forceinline__ void gemv_epilogue(const GemvArgs &a, int pair, int t
         break;
     }
     case EPI_ROPE_KV: {
-        const int r = pair * 2;
+        int r = pair * 2;
         // the qkv projection is materialised in the activation dtype before rope reads it
         float xa = round_act<T>(va), xb = round_act<T>(vb);
-        const int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
-        const int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
-        const int head = rr / a.dh, e = rr - head * a.dh;
+        int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
+        int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
+        int head = rr / a.dh, e = rr - head * a.dh;
+        uint32_t p = a.pos[t];
         if (sect < 2) {
-            const float ya = xa * pre.cs - xb * pre.sn, yb = xa * pre.sn + xb * pre.cs;
+            int half_dh = a.dh >> 1;
+            float sn = a.sin_t[(size_t)p * half_dh + (e >> 1)], cs = a.cos_t[(size_t)p * half_dh + (e >> 1)];
+            float ya = xa * cs - xb * sn, yb = xa * sn + xb * cs;
             xa = ya;
             xb = yb;
         }
-        const uint32_t packed = Act<T>::pack(xa, xb);
+        uint32_t packed = Act<T>::pack(xa, xb);
         if (sect == 0) {
             *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
         } else {
-            const int slot = tok.pos & (a.geom.page_tokens - 1);
-            const size_t off = a.geom.block_off(tok.page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
+            int seq = a.tok_seq[t];
+            int page = a.page_table[(size_t)seq * a.pt_stride + (p >> a.geom.page_shift)];
+            int slot = p & (a.geom.page_tokens - 1);
+            size_t off = a.geom.block_off(page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
             *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.kv_pool) + off) = packed;
         }
         break;
     }
     case EPI_SWIGLU: {
         // gate = row pair, up = row pair + di, both materialised before swiglu reads them
-        const float g = round_act<T>(va), u = round_act<T>(vb);
+        float g = round_act<T>(va), u = round_act<T>(vb);
         y[(size_t)t * a.stride_y + pair] = Act<T>::from_f(swiglu_act(g, u));
         break;
     }
     }
-}
-
-// the three steps in one call
-template <class T>
-__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
-    const EpiTok tok = gemv_epilogue_tok(a, t);
-    const EpiPre pre = gemv_epilogue_pre<T>(a, pair, t, tok);
-    gemv_epilogue<T>(a, pair, t, va, vb, tok, pre);
 }
 
 #endif  // __CUDACC__

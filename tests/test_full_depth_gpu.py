@@ -4,6 +4,15 @@ Config 2 (Llama-3.2-1B shape, bf16) and config 3 at batch 1 (Llama-3-8B shape, f
 vocabulary 128256, a 128-token prompt and 32 greedy steps against the CPU oracle on identical seeded
 weights (drawn on the GPU, copied to the host for the oracle).  Reports how many of the 32 steps pick
 the oracle's token exactly; a step that does not must sit on an oracle top-2 margin inside the logit error.
+
+Tolerance at full depth.  The 2e-2 (f16) / 8e-2 (bf16) bounds of the reduced-depth tests cannot hold here for
+ANY implementation with its own summation order: two CPU restatements that round at the same operator
+boundaries and differ only in the order of their f32 sums already disagree by 6.6e-3 / 1.5e-2 / 2.1e-2 at
+2 / 8 / 16 layers of the 8B widths (f16) and by 3.1e-2 / 5.7e-2 / 7.8e-2 for the 1B widths (bf16), over just
+4 steps x 4096 logits (tests/golden/noise_floor.json, made by tests/golden/noise_floor.py): a flipped rounding
+early on perturbs every later layer, and the difference grows about as the square root of the depth.  The
+bounds below are that floor extrapolated to the full depth and to the maximum over 32 steps x 128256 logits
+(about three times the 16-layer figure): 6e-2 for the 32-layer f16 model, 2e-1 for the 16-layer bf16 model.
 """
 import numpy as np
 import pytest
@@ -14,7 +23,7 @@ from helpers import device_weights, parity_report, teacher_forced_decode
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name,tol", [("llama1b", 8e-2), ("llama8b", 2e-2)])
+@pytest.mark.parametrize("name,tol", [("llama1b", 2e-1), ("llama8b", 6e-2)])
 def test_full_model_32_greedy_steps(L, O, name, tol):
     cfg = L.CONFIGS[name]
     steps = 32
