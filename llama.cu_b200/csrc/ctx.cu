@@ -844,12 +844,13 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             // scratch merge (many CTAs without work would sit in cluster barriers: 4.77 -> 5.75 ms at batch 32).
             static const int attn_cluster = getenv("LCU_ATTN_CLUSTER") ? atoi(getenv("LCU_ATTN_CLUSTER")) : 1;
             a.cluster_z = (attn_cluster && !batched && n_splits >= 2 && n_splits <= 8) ? n_splits : 0;
-            // decode rounds: cached rows of earlier rounds are fetched before the wait on the QKV projection
-            static const int attn_early = getenv("LCU_ATTN_EARLY") ? atoi(getenv("LCU_ATTN_EARLY")) : 1;
-            static const int attn_trigger = getenv("LCU_ATTN_TRIGGER") ? atoi(getenv("LCU_ATTN_TRIGGER")) : 1;
-            a.early_kv = (attn_early && r.decode_only) ? 1 : 0;
-            a.pdl_trigger = attn_trigger;
-            rc = attn_launch(a, dt, s, pdl || (!batched && (pdl_edges & 1)));
+            // launched as a programmatic dependent of the QKV projection (edge 0, off by default: it measured no
+            // gain, the GEMV's CTAs fill every register file until they leave) a decode round fetches the cached
+            // rows of earlier rounds before it waits; its own dependents start once its first tile has landed
+            const bool attn_pdl = pdl || (!batched && (pdl_edges & 1));
+            a.early_kv = (attn_pdl && r.decode_only) ? 1 : 0;
+            a.pdl_trigger = 1;
+            rc = attn_launch(a, dt, s, attn_pdl);
             if (rc) return rc;
             ++launches;
         }

@@ -32,7 +32,8 @@ def build(force=False):
         subprocess.run(["make", "-C", HERE, "liblcu_oracle.so"], check=True, capture_output=True)
     shim = os.path.join(HERE, "ref_shim.cu")
     if os.path.isdir(os.path.join(REF_DIR, "llama.cu", "src", "op")):
-        if force or not os.path.exists(REF_LIB) or os.path.getmtime(REF_LIB) < os.path.getmtime(shim):
+        step = os.path.join(HERE, "ref_step.cu")
+        if force or not os.path.exists(REF_LIB) or os.path.getmtime(REF_LIB) < max(os.path.getmtime(shim), os.path.getmtime(step)):
             subprocess.run(["make", "-C", HERE, "ref", f"REF_DIR={REF_DIR}"], check=True, capture_output=True)
     return LIB
 
