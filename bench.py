@@ -261,13 +261,18 @@ def tp_parity(L, env):
     out = torch.zeros(n, 2, dtype=torch.int32, device=env.dev)
     ids_equal, total, worst = 0, 0, 0.0
 
+    # columns of the vocabulary the lead rank's logits cover: all of them, or its own slice when the head is sharded
+    v_cols = cfg.vocab // env.world if (ctx.p2p_enabled and cfg.vocab % env.world == 0 and (cfg.vocab // env.world) % 2 == 0) else cfg.vocab
+
     def probe(i, s, lg, picked):
         nonlocal ids_equal, total, worst
         want_id = case["ids"][i][s]
         total += 1
-        ids_equal += int(picked == want_id)
+        ids_equal += int(picked == want_id)  # the arg-max over the WHOLE vocabulary either way
         cols = [0, 1, cfg.vocab // 2, cfg.vocab - 1, want_id]
-        worst = max(worst, float(np.abs(lg[cols] - np.array(case["logit_probes"][i][s])).max()))
+        for c, want in zip(cols, case["logit_probes"][i][s]):
+            if c < v_cols:
+                worst = max(worst, abs(float(lg[c]) - want))
 
     with torch.cuda.stream(stream):
         seqs = [ctx.seq_create() for _ in prompts]
@@ -275,14 +280,14 @@ def tp_parity(L, env):
             ctx.step([(seqs[i], 0, len(p))], p, out, stream=stream)
             stream.synchronize()
             if env.rank == 0:
-                probe(i, 0, ctx.logits(1)[0].float().cpu().numpy(), int(out[0, 0].item()))
+                probe(i, 0, ctx.logits(1).reshape(-1)[:v_cols].float().cpu().numpy(), int(out[0, 0].item()))
         pos = [len(p) for p in prompts]
         for s in range(steps - 1):
             ctx.step([(seqs[i], pos[i], 1) for i in range(n)], np.array([case["ids"][i][s] for i in range(n)], np.uint32),
                      out, stream=stream)
             stream.synchronize()
             if env.rank == 0:
-                lg = ctx.logits(n).float().cpu().numpy()
+                lg = ctx.logits(n).reshape(-1)[:n * v_cols].view(n, v_cols).float().cpu().numpy()
                 got = out[:n, 0].cpu().numpy().view(np.uint32)
                 for i in range(n):
                     probe(i, s + 1, lg[i], int(got[i]))
@@ -292,7 +297,8 @@ def tp_parity(L, env):
     status = env.status_all_ranks(ctx)
     transport = "peer memory" if ctx.p2p_enabled else "nccl"
     ctx.close()
-    return {"case": "llama8b_L2_tp (golden vectors, teacher-forced)", "transport": transport, "ids_equal": ids_equal,
+    return {"case": "llama8b_L2_tp (golden vectors, teacher-forced)", "transport": transport,
+            "lm_head": "sharded by vocabulary rows" if v_cols < cfg.vocab else "lead rank", "ids_equal": ids_equal,
             "steps": total, "max_logit_err": worst, "tolerance": 2e-2, "device_status_all_ranks": status,
             "ok": bool(ids_equal == total and worst <= 2e-2 and not any(status))}
 

@@ -156,7 +156,8 @@ LCU_API int lcu_seq_free(lcu_ctx *ctx, int seq);
  *   fast_map    n_fast pairs (index into the PREVIOUS round's out pairs, token slot): the
  *               slot's token is replaced on the device == `FastEmbedding` (op/fast_embedding.rs)
  * Under TP every rank calls this with the same arguments (the reference broadcasts them,
- * exec/group.rs:109-117); only rank 0 runs the head and writes out_dev. */
+ * exec/group.rs:109-117); only rank 0 writes out_dev (the head itself is sharded over the ranks in
+ * arg-max rounds of the peer-memory transport, see lcu_set_head_sharding). */
 LCU_API int lcu_step(lcu_ctx *ctx, lcu_stream_t stream, int n_req, const lcu_req *reqs, const uint32_t *tokens,
              const lcu_sample_args *args, const float *randoms, const uint32_t *fast_map, int n_fast,
              lcu_kv_pair *out_dev);
@@ -164,8 +165,24 @@ LCU_API int lcu_step(lcu_ctx *ctx, lcu_stream_t stream, int n_req, const lcu_req
 LCU_API const void *lcu_logits(const lcu_ctx *ctx);
 /* Device pointer to the hidden state (residual stream) of the last round, [n_tok, d]. */
 LCU_API const void *lcu_hidden(const lcu_ctx *ctx);
-/* Error word written by bounded device-side waits; 0 = none.  Synchronises `stream`. */
+/* Error word written by bounded device-side waits; 0 = none.  Synchronises `stream`.
+ * Bits: 4 = a tcgen05 / TMA pipeline wait ran out, 16 = a peer never delivered its part of an all-reduce (or its head
+ * candidates), 32 = the token broadcast never arrived.  The word is sticky: once this call has seen one of those bits,
+ * every later lcu_step of the context returns LCU_ERR_TIMEOUT (the rank group is out of step) until lcu_reset_status.
+ * (The reference has no counterpart: a missing rank blocks its NCCL call for ever, exec/engine.rs:272,339.) */
 LCU_API int lcu_device_status(lcu_ctx *ctx, lcu_stream_t stream, uint32_t *status_out);
+/* Clears the device status word and the sticky copy (synchronises the device). */
+LCU_API int lcu_reset_status(lcu_ctx *ctx);
+/* Longest any bounded wait on a peer (all-reduce arrival, token broadcast, head candidates) spins before it gives
+ * up and raises its status bit, in microseconds of SM clock at 2 GHz; default about two seconds.  Applies to every
+ * context on the device `ctx` lives on.  (No counterpart in the reference.) */
+LCU_API int lcu_set_wait_limit_us(lcu_ctx *ctx, long long us);
+/* Tensor parallelism over peer memory: 1 (default) = arg-max rounds shard the LM head by vocabulary rows — every rank
+ * streams vocab / tp rows and sends one candidate pair per request to the lead rank, which keeps the largest value
+ * (lowest index among equals, the reference's tie rule); 0 = the head runs on the lead rank alone, as in the reference
+ * (exec/engine.rs:90,201).  With sharding on, lcu_logits of the lead rank holds only its own vocab / tp columns
+ * [n_req, vocab / tp].  All ranks must use the same setting. */
+LCU_API int lcu_set_head_sharding(lcu_ctx *ctx, int enabled);
 /* 1 = replay decode rounds from a captured CUDA graph (default), 0 = launch eagerly
  * == the reference's `--no-cuda-graph` switch (xtask/src/main.rs:45-73). */
 LCU_API int lcu_set_cuda_graph(lcu_ctx *ctx, int enabled);

@@ -99,6 +99,9 @@ _SIGNATURES = {
     "lcu_logits": (C.c_void_p, [C.c_void_p]),
     "lcu_hidden": (C.c_void_p, [C.c_void_p]),
     "lcu_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
+    "lcu_reset_status": (C.c_int, [C.c_void_p]),
+    "lcu_set_wait_limit_us": (C.c_int, [C.c_void_p, C.c_longlong]),
+    "lcu_set_head_sharding": (C.c_int, [C.c_void_p, C.c_int]),
     "lcu_set_cuda_graph": (C.c_int, [C.c_void_p, C.c_int]),
     "lcu_set_megakernel": (C.c_int, [C.c_void_p, C.c_int]),
     "lcu_profile_counters": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
@@ -333,6 +336,15 @@ class Context:
         check(self.lib.lcu_device_status(self.h, stream_ptr(stream), C.byref(v)))
         return v.value
 
+    def reset_status(self):
+        check(self.lib.lcu_reset_status(self.h))
+
+    def set_wait_limit_us(self, us):
+        check(self.lib.lcu_set_wait_limit_us(self.h, int(us)))
+
+    def set_head_sharding(self, enabled):
+        check(self.lib.lcu_set_head_sharding(self.h, int(enabled)))
+
     def set_cuda_graph(self, enabled):
         check(self.lib.lcu_set_cuda_graph(self.h, int(enabled)))
 
@@ -384,4 +396,4 @@ def _view(address, n_elems, dt, device):
 
 from .model import (CONFIGS, ModelConfig, iter_synth_weights_torch, load_model, synth_weights_numpy,  # noqa: E402,F401
                     synth_weights_torch, tp_slice_numpy)
-from .host import Service, Session, generate  # noqa: E402,F401
+from .host import Service, Session, StepRendezvous, generate  # noqa: E402,F401

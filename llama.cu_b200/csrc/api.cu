@@ -68,6 +68,13 @@ int lcu_tp_slice_weight(const lcu_ctx *ctx, int kind, void *dst, const void *src
     const size_t eb = 2;
     const bool linear = kind == LCU_W_QKV || kind == LCU_W_O || kind == LCU_W_GATE_UP || kind == LCU_W_DOWN;
     LCU_REQUIRE(!(linear && c.weight_dtype == LCU_Q8_0 && c.tp_size > 1), "tp_slice_weight: slicing Q8_0 weights is not supported");
+    if (kind == LCU_W_LM_HEAD && c.tp_size > 1 && c.tp_rank != 0) {
+        // rows [rank * vocab / tp, (rank + 1) * vocab / tp) when the head can be sharded (lcu_weight_bytes says so)
+        const size_t bytes = lcu_weight_bytes(ctx, kind), full = (size_t)c.vocab * c.d * eb;
+        const size_t off = bytes < full ? (size_t)c.tp_rank * bytes : 0;
+        LCU_CHECK_CUDA(cudaMemcpyAsync(dst, reinterpret_cast<const unsigned char *>(src) + off, bytes, cudaMemcpyDeviceToDevice, s));
+        return LCU_OK;
+    }
     if (!linear || c.tp_size == 1) {
         LCU_CHECK_CUDA(cudaMemcpyAsync(dst, src, lcu_weight_bytes(ctx, kind), cudaMemcpyDeviceToDevice, s));
         return LCU_OK;

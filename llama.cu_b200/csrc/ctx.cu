@@ -132,6 +132,11 @@ struct lcu_ctx {
     // tensor parallelism over peer memory (set up by lcu_p2p_create / lcu_p2p_attach)
     P2pState p2p;
 
+    // LM head sharded by vocabulary rows under tensor parallelism (peer-memory transport, arg-max rounds)
+    bool head_shard = true;           // lcu_set_head_sharding
+    lcu_kv_pair *head_local = nullptr;  // this rank's candidates
+    uint32_t sticky_status = 0;       // last value lcu_device_status read
+
     bool use_graph = true;
     std::map<std::vector<int>, StepGraph> graphs;
     int last_launches = 0;
@@ -216,10 +221,19 @@ static int batched_min_tokens() {
     return v;
 }
 
+// Rows of the LM head one rank holds when the head is sharded by vocabulary (0: the shape does not allow it).
+static int head_rows_per_rank(const lcu_ctx *c) {
+    if (c->tp_size <= 1 || c->desc.vocab % c->tp_size) return 0;
+    const int v = c->desc.vocab / c->tp_size;
+    return v % 2 ? 0 : v;
+}
+
 static size_t weight_elems(const lcu_ctx *c, int kind) {
     const lcu_model_desc &d = c->desc;
     switch (kind) {
-    case LCU_W_EMBD: case LCU_W_LM_HEAD: return (size_t)d.vocab * d.d;
+    case LCU_W_EMBD: return (size_t)d.vocab * d.d;
+    case LCU_W_LM_HEAD:  // the lead rank keeps the whole matrix (sampling rounds need every logit), the others their rows
+        return (size_t)(c->tp_rank != 0 && head_rows_per_rank(c) ? head_rows_per_rank(c) : d.vocab) * d.d;
     case LCU_W_ATTN_NORM: case LCU_W_FFN_NORM: case LCU_W_OUT_NORM: return (size_t)d.d;
     case LCU_W_QKV: return (size_t)(c->qd + 2 * c->kvd) * d.d;
     case LCU_W_O: return (size_t)d.d * c->qd;
@@ -361,6 +375,7 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     sz_attn = align256(sz_attn + 256);
     c->sample_ws_bytes = align256(sample_workspace_bytes(c->max_seqs, (size_t)d.vocab));
     size_t sz_pairs = align256((size_t)c->max_tokens * sizeof(lcu_kv_pair));
+    size_t sz_head_local = align256((size_t)c->max_seqs * sizeof(lcu_kv_pair));
     c->desc_cap = align256(desc_layout(c->max_tokens, c->max_seqs, c->pt_stride).total);
     const int grid = sm_count();
     size_t sz_mk_part = align256((size_t)4 * c->nh_l * 16 * (d.dh + 2) * 4);
@@ -368,7 +383,7 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     size_t sz_mk_phases = align256((size_t)(d.n_layers * 5 + 1) * sizeof(MkPhase));
     const size_t sz_sk_ws = (size_t)16 << 20, sz_sk_tickets = (size_t)16 << 10;
     size_t total = sz_x + 2 * sz_q + sz_act + sz_logits + sz_attn + c->sample_ws_bytes + sz_pairs + 512 + c->desc_cap +
-                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases + sz_x + sz_sk_ws + sz_sk_tickets;
+                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases + sz_x + sz_sk_ws + sz_sk_tickets + sz_head_local;
     cudaError_t e = cudaMalloc(&c->arena, total);
     if (e != cudaSuccess) {
         delete c;
@@ -395,7 +410,8 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     c->mk_phases_dev = reinterpret_cast<MkPhase *>(p); p += sz_mk_phases;
     c->hbuf = p; p += sz_x;
     c->sk_ws = p; p += sz_sk_ws;
-    c->sk_tickets = reinterpret_cast<unsigned *>(p);
+    c->sk_tickets = reinterpret_cast<unsigned *>(p); p += sz_sk_tickets;
+    c->head_local = reinterpret_cast<lcu_kv_pair *>(p);
     c->sk_ws_bytes = sz_sk_ws;
     for (int i = 0; i < lcu_ctx::RING; ++i) {
         e = cudaMallocHost(reinterpret_cast<void **>(&c->desc_host[i]), c->desc_cap);
@@ -634,6 +650,25 @@ int lcu_profile_counters(lcu_ctx *c, int enable, long long *out16) {
     }
     return LCU_OK;
 }
+int lcu_set_head_sharding(lcu_ctx *c, int enabled) {
+    LCU_REQUIRE(c, "set_head_sharding: null context");
+    if (c->head_shard != (enabled != 0)) drop_graphs(c);
+    c->head_shard = enabled != 0;
+    return LCU_OK;
+}
+int lcu_set_wait_limit_us(lcu_ctx *c, long long us) {
+    LCU_REQUIRE(c, "set_wait_limit_us: null context");
+    LCU_CHECK_CUDA(cudaSetDevice(c->device));
+    return p2p_set_wait_limit_us(us);
+}
+int lcu_reset_status(lcu_ctx *c) {
+    LCU_REQUIRE(c, "reset_status: null context");
+    LCU_CHECK_CUDA(cudaSetDevice(c->device));
+    LCU_CHECK_CUDA(cudaDeviceSynchronize());
+    LCU_CHECK_CUDA(cudaMemset(c->dev_status, 0, 4));
+    c->sticky_status = 0;
+    return LCU_OK;
+}
 int lcu_last_launch_count(const lcu_ctx *c) { return c ? c->last_launches : 0; }
 double lcu_last_step_bytes(const lcu_ctx *c) { return c ? c->last_bytes : 0.0; }
 const void *lcu_logits(const lcu_ctx *c) { return c ? c->logits : nullptr; }
@@ -643,6 +678,7 @@ int lcu_device_status(lcu_ctx *c, lcu_stream_t stream, uint32_t *status_out) {
     LCU_REQUIRE(c && status_out, "device_status: null argument");
     LCU_CHECK_CUDA(cudaMemcpyAsync(status_out, c->dev_status, 4, cudaMemcpyDeviceToHost, as_stream(stream)));
     LCU_CHECK_CUDA(cudaStreamSynchronize(as_stream(stream)));
+    c->sticky_status = *status_out;
     return LCU_OK;
 }
 
@@ -762,6 +798,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     const int scatter_cols = (p2p && c->tp_size >= scatter_ranks && (long)r.n_tok * d.d * 2 >= scatter_min &&
                               d.d % (c->tp_size * 8) == 0) ? d.d / c->tp_size : 0;
     c->p2p.parity = 0;  // every step holds an even number of all-reduces, so captured graphs agree on it
+    static const bool reduce_pdl = !(getenv("LCU_P2P_REDUCE_PDL") && getenv("LCU_P2P_REDUCE_PDL")[0] == '0');
     int linear_ctas = 0;  // CTAs of the launches of the last `linear` call
     auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
                       const void *norm_w, bool push = false, int edge_in = -1, int edge_out = -1) -> int {
@@ -810,11 +847,14 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
         return LCU_OK;
     };
     // sum of every rank's partial of the residual stream: fused peer-memory form, or ncclAllReduce
-    auto all_reduce_x = [&]() -> int {
+    // edge_out: the layer edge the producing projection releases its dependents on (the reduction then starts as
+    // their programmatic dependent, spinning on the arrival counter while the producers drain)
+    auto all_reduce_x = [&](int edge_out) -> int {
         if (c->tp_size == 1) return LCU_OK;
         ++launches;
         if (p2p)
-            return p2p_reduce_launch(c->p2p, c->x, r.n_tok, d.d, dt, (unsigned)(c->tp_size * linear_ctas), scatter_cols, c->dev_status, s);
+            return p2p_reduce_launch(c->p2p, c->x, r.n_tok, d.d, dt, (unsigned)(c->tp_size * linear_ctas), scatter_cols, c->dev_status, s,
+                                     reduce_pdl && (pdl || ((pdl_edges >> edge_out) & 1)));
         return lcu_op_all_reduce(c, c->x, c->x, (size_t)r.n_tok * d.d, dt, reinterpret_cast<lcu_stream_t>(s));
     };
     for (int l = 0; l < d.n_layers; ++l) {
@@ -864,7 +904,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             rc = linear(a, r.n_tok, c->att, c->qd, c->x, d.d, false, nullptr, p2p, 1, 2);
             if (rc) return rc;
         }
-        rc = all_reduce_x();
+        rc = all_reduce_x(2);
         if (rc) return rc;
         // --- RMSNorm + gate|up projection + SwiGLU
         {
@@ -885,12 +925,17 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             rc = linear(a, r.n_tok, c->act, c->di_l, c->x, d.d, false, nullptr, p2p, 3, l + 1 < d.n_layers ? 4 : 5);
             if (rc) return rc;
         }
-        rc = all_reduce_x();
+        rc = all_reduce_x(l + 1 < d.n_layers ? 4 : 5);
         if (rc) return rc;
     }
 
-    // --- head on the lead rank only (exec/engine.rs:90,201): gather + RMSNorm + LM head + sampling
-    if (c->tp_rank == 0) {
+    // --- head (exec/engine.rs:90,201): gather + RMSNorm + LM head + sampling.  The reference runs it on the lead rank
+    // alone; with the peer-memory transport an arg-max round shards it by vocabulary rows instead: every rank streams
+    // vocab / tp rows, arg-maxes them, the lead rank keeps the best candidate per row (lowest index among equals).
+    const int v_rows = head_rows_per_rank(c);
+    const bool head_sharded = p2p && c->head_shard && v_rows > 0 && !r.any_sampling;
+    if (c->tp_rank == 0 || head_sharded) {
+        const int vocab_l = head_sharded ? v_rows : d.vocab;  // the lead rank's slice is the first rows of its full matrix
         const bool head_batched = c->batched_ok && r.n_req >= batched_min_tokens();
         if (head_batched) {
             // gather the output rows (Embedding reused as a row gather, exec/output_head.rs:75-77), norm, LM head
@@ -902,8 +947,8 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
                 GemvArgs a{};
                 a.w = c->lm_head; a.w_q8 = 0;
                 a.x = row(c->hbuf, d.d, r0); a.stride_x = d.d; a.n_tok = r.n_req - r0 < 64 ? r.n_req - r0 : 64;
-                a.in = d.d; a.out = d.vocab; a.prologue = PRO_NONE; a.epilogue = EPI_STORE;
-                a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
+                a.in = d.d; a.out = vocab_l; a.prologue = PRO_NONE; a.epilogue = EPI_STORE;
+                a.y = row(c->logits, vocab_l, r0); a.stride_y = vocab_l;
                 const bool tc = tc_on && a.n_tok > 8 && gemm_tc_supported(a.in, 0);
                 rc = tc ? gemm_tc_launch(a, dt, s, pdl) : gemm_skinny_launch(a, dt, s, pdl);
                 if (rc) return rc;
@@ -916,20 +961,28 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (nt == 3) nt = 2;
             GemvArgs a{};
             a.w = c->lm_head; a.w_q8 = 0;
-            a.x = c->x; a.stride_x = d.d; a.x_rows = out_idx + r0; a.n_tok = nt; a.in = d.d; a.out = d.vocab;
+            a.x = c->x; a.stride_x = d.d; a.x_rows = out_idx + r0; a.n_tok = nt; a.in = d.d; a.out = vocab_l;
             a.prologue = PRO_RMSNORM; a.norm_w = c->out_norm; a.norm_f32 = d.norm_dtype == LCU_F32; a.eps = d.eps;
-            a.epilogue = EPI_STORE; a.y = row(c->logits, d.vocab, r0); a.stride_y = d.vocab;
-            const bool head_pdl = pdl || (((pdl_edges >> 5) & 1) && c->tp_size == 1);
+            a.epilogue = EPI_STORE; a.y = row(c->logits, vocab_l, r0); a.stride_y = vocab_l;
+            // after the last layer's reduction (tensor parallelism) or its down projection
+            const bool head_pdl = pdl || (((pdl_edges >> 5) & 1) && (c->tp_size == 1 || (p2p && reduce_pdl)));
             a.pdl_trigger = pdl_trigger; a.early_prefetch = (head_pdl && early_prefetch == 1) ? 3 : early_prefetch;
             rc = gemv_launch(a, dt, s, head_pdl);
             if (rc) return rc;
             ++launches;
             r0 += nt;
         }
-        rc = sample_rows(out_dev, c->pre_pairs, c->logits, r.n_req, (size_t)d.vocab, r.any_sampling ? args : nullptr,
-                         randoms, dt, c->sample_ws, c->sample_ws_bytes, s, pdl, r.any_sampling);
+        lcu_kv_pair *pairs_out = head_sharded ? c->head_local : out_dev;
+        rc = sample_rows(pairs_out, head_sharded ? nullptr : c->pre_pairs, c->logits, r.n_req, (size_t)vocab_l,
+                         r.any_sampling ? args : nullptr, randoms, dt, c->sample_ws, c->sample_ws_bytes, s, pdl, r.any_sampling);
         if (rc) return rc;
         launches += r.any_sampling ? 3 : 2;
+        if (head_sharded) {
+            rc = c->tp_rank == 0 ? p2p_head_pick_launch(c->p2p, c->head_local, r.n_req, dt, out_dev, c->pre_pairs, c->dev_status, s)
+                                 : p2p_head_push_launch(c->p2p, c->head_local, r.n_req, (uint32_t)(c->tp_rank * v_rows), s);
+            if (rc) return rc;
+            ++launches;
+        }
     }
     *count = launches;
     return LCU_OK;
@@ -1006,9 +1059,12 @@ extern "C" int lcu_p2p_create(lcu_ctx *c, void *handle64_out) {
     st.rank = c->tp_rank;
     st.n = c->tp_size;
     st.slot_bytes = ((size_t)c->max_tokens * c->desc.d * 2 + 255) / 256 * 256;
-    const size_t bcast = (size_t)c->max_tokens * 4;
-    st.hdr_bytes = p2p_header_bytes(bcast);
-    const size_t bytes = p2p_region_bytes(st.n, st.slot_bytes, bcast);
+    const size_t bcast = (((size_t)c->max_tokens * 4 + 15) / 16) * 16;
+    const size_t cand = (size_t)P2P_MAX_RANKS * c->max_seqs * sizeof(lcu_kv_pair);
+    st.hdr_bytes = p2p_header_bytes(bcast, cand);
+    st.cand_off = 256 + bcast;
+    st.max_seqs = c->max_seqs;
+    const size_t bytes = p2p_region_bytes(st.n, st.slot_bytes, bcast, cand);
     LCU_CHECK_CUDA(cudaMalloc(&st.own, bytes));
     LCU_CHECK_CUDA(cudaMemset(st.own, 0, bytes));
     LCU_CHECK_CUDA(cudaDeviceSynchronize());
@@ -1049,7 +1105,12 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
     const lcu_model_desc &d = c->desc;
     LCU_REQUIRE(d.vocab % 2 == 0, "step: vocab %d must be even", d.vocab);
     if (!c->pool) { set_error("step: no KV pool"); return LCU_ERR_STATE; }
-    if (!c->embd || (c->tp_rank == 0 && (!c->out_norm || !c->lm_head))) { set_error("step: embedding / output weights missing"); return LCU_ERR_STATE; }
+    const bool head_everywhere = c->p2p.ready && c->head_shard && head_rows_per_rank(c) > 0;
+    if (!c->embd || ((c->tp_rank == 0 || head_everywhere) && (!c->out_norm || !c->lm_head))) { set_error("step: embedding / output weights missing"); return LCU_ERR_STATE; }
+    if (c->sticky_status & (4u | 16u | 32u)) {
+        set_error("step: a bounded device-side wait ran out earlier (status %u); the group is broken until lcu_reset_status", c->sticky_status);
+        return LCU_ERR_TIMEOUT;
+    }
     for (int l = 0; l < d.n_layers; ++l) {
         const LayerWeights &W = c->layers[l];
         if (!W.attn_norm || !W.qkv || !W.o || !W.ffn_norm || !W.gate_up || !W.down) {
@@ -1141,7 +1202,9 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
     {
         double wb = d.weight_dtype == LCU_Q8_0 ? 34.0 / 32.0 : 2.0;
         double per_layer = ((double)(c->qd + 2 * c->kvd) * d.d + (double)d.d * c->qd + 2.0 * c->di_l * d.d + (double)d.d * c->di_l) * wb;
-        double bytes = per_layer * d.n_layers + (c->tp_rank == 0 ? (double)d.vocab * d.d * 2.0 : 0.0);
+        const bool sharded = head_everywhere && !any_sampling;
+        double bytes = per_layer * d.n_layers + (sharded ? (double)head_rows_per_rank(c) * d.d * 2.0
+                                                         : (c->tp_rank == 0 ? (double)d.vocab * d.d * 2.0 : 0.0));
         for (int i = 0; i < n_req; ++i)
             for (uint32_t j = 0; j < reqs[i].len; ++j)
                 bytes += (double)(reqs[i].pos + j + 1) * 2.0 * c->kvd * d.n_layers * 2.0;
@@ -1166,7 +1229,7 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
         return rc;
     }
     std::vector<int> key = {n_req, n_tok, n_fast, any_sampling ? 1 : 0, (int)((uintptr_t)out_dev & 0x7fffffff),
-                            (int)((uintptr_t)out_dev >> 31), use_mk ? 1 : 0};
+                            (int)((uintptr_t)out_dev >> 31), use_mk ? 1 : 0, c->head_shard ? 1 : 0};
     auto it = c->graphs.find(key);
     if (it == c->graphs.end()) {
         cudaGraph_t graph = nullptr;

@@ -1,5 +1,7 @@
 // Local half of the peer-memory all-reduce (protocol in p2p.cuh): wait for every rank's partial, sum
 // the slots in rank order, write the residual stream, re-arm the counter.
+#include <cstring>
+
 #include "common.cuh"
 #include "p2p.cuh"
 
@@ -7,7 +9,10 @@ namespace lcu {
 
 namespace {
 
-constexpr long long P2P_WAIT_CYCLES = 4000000000ll;  // about two seconds of SM clock
+// Longest a kernel here spins on a peer before it gives up: about two seconds of SM clock unless the host set
+// another limit (p2p_set_wait_limit_us; kept in constant memory so that captured graphs see a later change too).
+__constant__ long long c_wait_cycles = 4000000000ll;
+__device__ __forceinline__ long long p2p_wait_cycles() { return c_wait_cycles; }
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     unsigned v;
@@ -24,10 +29,11 @@ template <class T>
 __global__ void __launch_bounds__(256) p2p_reduce_kernel(unsigned *header, int parity, ReduceSrc src, int n_ranks, T *y,
                                                          size_t n_vec, unsigned expected, uint32_t *status) {
     unsigned *arrive = header + parity, *leave = header + 2 + parity;
+    grid_dep_launch();
     if (threadIdx.x == 0) {
         const long long t0 = clock64();
         // once a wait has run out the group is broken: later waits give up at once instead of adding seconds each
-        const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : P2P_WAIT_CYCLES;
+        const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : p2p_wait_cycles();
         while (ld_acquire_sys(arrive) < expected) {
             if (clock64() - t0 > limit) {  // a peer never pushed: report and carry on
                 atomicOr(status, 16u);
@@ -79,7 +85,8 @@ __global__ void __launch_bounds__(256) p2p_reduce_scatter_kernel(unsigned *heade
                                                                  int n_ranks, int rank, T *y, int n_tok, int d, int cols,
                                                                  unsigned expected, uint32_t *status) {
     unsigned *arrive = header + parity, *leave = header + 2 + parity, *garrive = header + 5 + parity;
-    const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : P2P_WAIT_CYCLES;
+    grid_dep_launch();
+    const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : p2p_wait_cycles();
     if (threadIdx.x == 0) {
         const long long t0 = clock64();
         while (ld_acquire_sys(arrive) < expected) {
@@ -171,7 +178,7 @@ __global__ void __launch_bounds__(256) p2p_broadcast_kernel(BcastDst peers, int 
     unsigned *flag = reinterpret_cast<unsigned *>(peers.base[rank]) + 4;
     if (threadIdx.x == 0) {
         const long long t0 = clock64();
-        const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : P2P_WAIT_CYCLES;
+        const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : p2p_wait_cycles();
         while (ld_acquire_sys(flag) == 0u) {
             if (clock64() - t0 > limit) {
                 atomicOr(status, 32u);
@@ -187,11 +194,67 @@ __global__ void __launch_bounds__(256) p2p_broadcast_kernel(BcastDst peers, int 
     if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned *>(flag) = 0u;
 }
 
+// ---- LM head sharded by vocabulary rows: candidates of the other ranks travel to the lead rank
+__global__ void __launch_bounds__(64) p2p_head_push_kernel(lcu_kv_pair *dst, unsigned *counter, const lcu_kv_pair *local, int rows,
+                                                           uint32_t idx_offset) {
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        lcu_kv_pair p = local[i];
+        p.idx += idx_offset;
+        dst[i] = p;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd_system(counter, 1u);
+}
+
+template <class T>
+__global__ void __launch_bounds__(64) p2p_head_pick_kernel(const lcu_kv_pair *cands, unsigned *counter, int n_ranks, int max_seqs,
+                                                           const lcu_kv_pair *local, int rows, lcu_kv_pair *out,
+                                                           lcu_kv_pair *out_copy, uint32_t *status) {
+    if (threadIdx.x == 0) {
+        const long long t0 = clock64();
+        const long long limit = (*reinterpret_cast<volatile uint32_t *>(status) & 48u) ? 20000ll : p2p_wait_cycles();
+        while (ld_acquire_sys(counter) < (unsigned)(n_ranks - 1)) {
+            if (clock64() - t0 > limit) {  // a rank never delivered its candidates: report, keep the local winner
+                atomicOr(status, 16u);
+                break;
+            }
+            __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        lcu_kv_pair best = local[i];
+        float bv = Act<T>::to_f(*reinterpret_cast<const T *>(&best.val));
+        for (int r = 1; r < n_ranks; ++r) {
+            const unsigned long long raw = __ldcg(reinterpret_cast<const unsigned long long *>(cands + (size_t)r * max_seqs + i));
+            lcu_kv_pair c;
+            memcpy(&c, &raw, 8);
+            const float cv = Act<T>::to_f(*reinterpret_cast<const T *>(&c.val));
+            if (cv > bv || (cv == bv && c.idx < best.idx)) { best = c; bv = cv; }
+        }
+        out[i] = best;
+        if (out_copy) out_copy[i] = best;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        *reinterpret_cast<volatile unsigned *>(counter) = 0u;
+        __threadfence();
+    }
+}
+
 }  // namespace
 
-size_t p2p_header_bytes(size_t bcast_bytes) { return (256 + bcast_bytes + 255) / 256 * 256; }
-size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes) {
-    return p2p_header_bytes(bcast_bytes) + (size_t)2 * n_ranks * slot_bytes + (size_t)2 * slot_bytes;
+int p2p_set_wait_limit_us(long long us) {
+    LCU_REQUIRE(us >= 1 && us <= 60ll * 1000 * 1000, "wait limit of %lld us (1 us .. 60 s)", us);
+    const long long cycles = us * 2000;  // SM clock of this part tops out just under 2 GHz
+    LCU_CHECK_CUDA(cudaMemcpyToSymbol(c_wait_cycles, &cycles, sizeof(cycles)));
+    return LCU_OK;
+}
+
+size_t p2p_header_bytes(size_t bcast_bytes, size_t cand_bytes) { return (256 + bcast_bytes + cand_bytes + 255) / 256 * 256; }
+size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes, size_t cand_bytes) {
+    return p2p_header_bytes(bcast_bytes, cand_bytes) + (size_t)2 * n_ranks * slot_bytes + (size_t)2 * slot_bytes;
 }
 
 static inline unsigned char *slot_ptr(void *base, const P2pState &st, int parity, int src) {
@@ -212,7 +275,7 @@ void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push, int scatt
 }
 
 int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned expected, int scatter_cols, uint32_t *status,
-                      cudaStream_t s) {
+                      cudaStream_t s, bool pdl) {
     const size_t elems = (size_t)n_tok * d;
     LCU_REQUIRE(st.ready, "p2p all-reduce: peers are not attached");
     LCU_REQUIRE(elems % 8 == 0 && elems * 2 <= st.slot_bytes, "p2p all-reduce: %zu elements do not fit the slot", elems);
@@ -232,11 +295,11 @@ int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned 
         if (grid > 32) grid = 32;
         if (grid < 1) grid = 1;
         if (dt == LCU_BF16)
-            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, false, header, st.parity,
+            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, pdl, header, st.parity,
                                          src, dst, st.n, st.rank, reinterpret_cast<__nv_bfloat16 *>(y), n_tok, d, scatter_cols,
                                          expected, status));
         else
-            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__half>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src,
+            LCU_CHECK_CUDA(launch_kernel(p2p_reduce_scatter_kernel<__half>, dim3(grid), dim3(256), 0, s, pdl, header, st.parity, src,
                                          dst, st.n, st.rank, reinterpret_cast<__half *>(y), n_tok, d, scatter_cols, expected,
                                          status));
         st.parity ^= 1;
@@ -246,12 +309,38 @@ int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned 
     int grid = (int)((n_vec + 255) / 256);
     if (grid > 64) grid = 64;
     if (dt == LCU_BF16)
-        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src, st.n,
+        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, pdl, header, st.parity, src, st.n,
                                      reinterpret_cast<__nv_bfloat16 *>(y), n_vec, expected, status));
     else
-        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__half>, dim3(grid), dim3(256), 0, s, false, header, st.parity, src, st.n,
+        LCU_CHECK_CUDA(launch_kernel(p2p_reduce_kernel<__half>, dim3(grid), dim3(256), 0, s, pdl, header, st.parity, src, st.n,
                                      reinterpret_cast<__half *>(y), n_vec, expected, status));
     st.parity ^= 1;
+    return LCU_OK;
+}
+
+int p2p_head_push_launch(P2pState &st, const void *local_pairs, int rows, uint32_t idx_offset, cudaStream_t s) {
+    LCU_REQUIRE(st.ready && st.rank != 0 && rows <= st.max_seqs, "p2p head push: bad state (rank %d, %d rows)", st.rank, rows);
+    unsigned char *lead = reinterpret_cast<unsigned char *>(st.base[0]);
+    lcu_kv_pair *dst = reinterpret_cast<lcu_kv_pair *>(lead + st.cand_off) + (size_t)st.rank * st.max_seqs;
+    LCU_CHECK_CUDA(launch_kernel(p2p_head_push_kernel, dim3(1), dim3(64), 0, s, false, dst, reinterpret_cast<unsigned *>(lead) + 7,
+                                 reinterpret_cast<const lcu_kv_pair *>(local_pairs), rows, idx_offset));
+    return LCU_OK;
+}
+
+int p2p_head_pick_launch(P2pState &st, const void *local_pairs, int rows, int dt, void *out, void *out_copy, uint32_t *status,
+                         cudaStream_t s) {
+    LCU_REQUIRE(st.ready && st.rank == 0 && rows <= st.max_seqs, "p2p head pick: bad state (rank %d, %d rows)", st.rank, rows);
+    unsigned char *own = reinterpret_cast<unsigned char *>(st.own);
+    const lcu_kv_pair *cands = reinterpret_cast<const lcu_kv_pair *>(own + st.cand_off);
+    unsigned *counter = reinterpret_cast<unsigned *>(own) + 7;
+    if (dt == LCU_BF16)
+        LCU_CHECK_CUDA(launch_kernel(p2p_head_pick_kernel<__nv_bfloat16>, dim3(1), dim3(64), 0, s, false, cands, counter, st.n,
+                                     st.max_seqs, reinterpret_cast<const lcu_kv_pair *>(local_pairs), rows,
+                                     reinterpret_cast<lcu_kv_pair *>(out), reinterpret_cast<lcu_kv_pair *>(out_copy), status));
+    else
+        LCU_CHECK_CUDA(launch_kernel(p2p_head_pick_kernel<__half>, dim3(1), dim3(64), 0, s, false, cands, counter, st.n, st.max_seqs,
+                                     reinterpret_cast<const lcu_kv_pair *>(local_pairs), rows, reinterpret_cast<lcu_kv_pair *>(out),
+                                     reinterpret_cast<lcu_kv_pair *>(out_copy), status));
     return LCU_OK;
 }
 

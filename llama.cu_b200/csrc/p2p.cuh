@@ -54,23 +54,38 @@ struct P2pState {
     void *own = nullptr;                     // this rank's region (cudaMalloc)
     void *base[P2P_MAX_RANKS] = {nullptr};   // every rank's region as mapped here
     size_t slot_bytes = 0;                   // max_tokens * d * 2
-    size_t hdr_bytes = 0;                    // counters (first 256 bytes) + broadcast buffer
+    size_t hdr_bytes = 0;                    // counters (first 256 bytes) + broadcast buffer + head candidates
+    size_t cand_off = 0;                     // byte offset of the head candidates [n_ranks][max_seqs] (8 bytes each)
+    int max_seqs = 0;
     int parity = 0;                          // of the next all-reduce
     bool ready = false;
 };
 
 // Region layout: words 0..1 arrival counters, 2..3 departure tickets (per parity), 4 broadcast flag, 5..6 second
-// (gather) counters; from byte 256 the broadcast buffer (bcast_bytes); from hdr_bytes the slots
-// [2][n_ranks][slot_bytes], then the gather buffers [2][slot_bytes].
-size_t p2p_header_bytes(size_t bcast_bytes);
-size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes);
+// (gather) counters, 7 head-candidate counter; from byte 256 the broadcast buffer (bcast_bytes), then the head
+// candidates (cand_bytes); from hdr_bytes the slots [2][n_ranks][slot_bytes], then the gather buffers [2][slot_bytes].
+size_t p2p_header_bytes(size_t bcast_bytes, size_t cand_bytes);
+size_t p2p_region_bytes(int n_ranks, size_t slot_bytes, size_t bcast_bytes, size_t cand_bytes);
 // Fills `push` for the next all-reduce (current parity) with a byte offset into the slot; scatter_cols as in P2pPush.
 void p2p_make_push(const P2pState &st, size_t byte_off, P2pPush *push, int scatter_cols = 0);
 // Enqueues the local reduction of n_tok rows of d elements (2-byte activation type): waits for `expected` arrivals,
 // y = sum over ranks of the slots (scatter_cols != 0: the scatter form above); then flips the parity.
 // status: device word that gets bit 16 on a timed-out wait.
+// pdl: launched as a programmatic dependent of the producing projection — the kernel only spins on counters that the
+// producers (this rank's included) raise after their last access, so it never waits for the producer grid itself, and
+// it releases its own dependents at once.
 int p2p_reduce_launch(P2pState &st, void *y, int n_tok, int d, int dt, unsigned expected, int scatter_cols, uint32_t *status,
-                      cudaStream_t s);
+                      cudaStream_t s, bool pdl = false);
+
+// LM head sharded by vocabulary rows: every rank arg-maxes its slice; the others store their candidate pairs (index made
+// global) into the lead rank's region and raise its counter (push), the lead rank waits (bounded) for n_ranks - 1
+// arrivals and keeps, per row, the largest value / lowest index (pick), writing `out` and `out_copy`.
+int p2p_head_push_launch(P2pState &st, const void *local_pairs, int rows, uint32_t idx_offset, cudaStream_t s);
+int p2p_head_pick_launch(P2pState &st, const void *local_pairs, int rows, int dt, void *out, void *out_copy, uint32_t *status,
+                         cudaStream_t s);
+
+// Limit of every bounded peer wait of the calling thread's current device, in microseconds (default about 2 s).
+int p2p_set_wait_limit_us(long long us);
 
 // Token broadcast from rank `root` (the reference's `share_inputs`, exec/engine.rs:264-274): the root stores
 // `bytes` (a multiple of 4, at most the broadcast buffer) into every other rank's buffer and raises their flag;

@@ -192,3 +192,40 @@ def _generate(svc, ctx, prompts, steps, sample_args, read_every_step, randoms):
     for s in sessions:
         ctx.seq_free(s.seq)
     return [toks[s.id] for s in sessions]
+
+
+class StepRendezvous:
+    """Host-side roll call of the tensor-parallel ranks before a round is launched.
+
+    The reference keeps its per-GPU worker threads in step with a `Barrier` (llama.cu/src/exec/engine.rs:272,339),
+    which blocks for ever when a worker has died.  With one process per GPU the ranks meet through a key-value
+    store (`torch.distributed.TCPStore` / `FileStore` / the store of an initialised process group): every rank
+    marks its arrival at round `step`, then waits until all have — or until `timeout_s` has passed, in which case
+    it raises LcuError(ERR_TIMEOUT) naming the ranks that never arrived, BEFORE anything is launched on the GPU.
+    (The kernels' own bounded waits are the second line of defence, see lcu_device_status.)"""
+
+    def __init__(self, store, rank, world, timeout_s=5.0, prefix="lcu/round"):
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+
+    def _key(self, step, rank):
+        return f"{self.prefix}/{step}/{rank}"
+
+    def arrive(self, step):
+        self.store.set(self._key(step, self.rank), b"1")
+
+    def missing(self, step):
+        """Ranks that have not arrived at `step` (non-blocking)."""
+        return [r for r in range(self.world) if not self.store.check([self._key(step, r)])]
+
+    def wait(self, step, timeout_s=None):
+        import time
+        from . import ERR_TIMEOUT, LcuError
+        limit = time.monotonic() + (self.timeout_s if timeout_s is None else timeout_s)
+        self.arrive(step)
+        while True:
+            gone = self.missing(step)
+            if not gone:
+                return
+            if time.monotonic() > limit:
+                raise LcuError(ERR_TIMEOUT, f"round {step}: rank(s) {gone} never arrived")
+            time.sleep(0.002)

@@ -204,11 +204,11 @@ def load_model(cfg, weights, device=0, kv_bytes=None, tp_rank=0, tp_size=1, comm
             t = torch.from_numpy(w.view(np.int16)).to(dev)
         else:
             t = w
-        if tp_size > 1 and kind in LINEAR_KINDS:
+        # linear weights are cut per rank; the LM head stays whole on the lead rank and is cut by vocabulary rows on
+        # the others (used when arg-max rounds shard the head, see lcu_set_head_sharding)
+        if tp_size > 1 and (kind in LINEAR_KINDS or (kind == W_LM_HEAD and tp_rank != 0)):
             t = ctx.tp_slice(kind, t)
             torch.cuda.synchronize(device)
-        if tp_size > 1 and tp_rank != 0 and kind == W_LM_HEAD:
-            continue  # the head runs on the lead rank only
         ctx.set_weight(max(layer, 0), kind, t)
     if kv_bytes is None:
         kv_bytes = 64 * ctx.page_bytes

@@ -20,6 +20,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LENGTHS = (5, 9, 40)
 
 
+def spec_with(spec_path, tmp_path, **kw):
+    spec = json.load(open(spec_path))
+    spec.update(kw)
+    path = tmp_path / ("spec_" + "_".join(f"{k}{v}" for k, v in kw.items()) + ".json")
+    json.dump(spec, open(path, "w"))
+    return path
+
+
 def run_world(world, spec_path, tmp_path, mode, extra_env=None, tag=""):
     out = tmp_path / f"tp{world}_{mode}{tag}.npz"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
@@ -34,9 +42,10 @@ def run_world(world, spec_path, tmp_path, mode, extra_env=None, tag=""):
 
 def compare(tag, got, o_ids, o_lgs, one, tol, log):
     """Unconditional checks of one run against the oracle and against TP=1."""
-    lg = got["logits"]
-    err_oracle = float(np.abs(lg - o_lgs).max())
-    err_tp1 = float(np.abs(lg - one["logits"]).max()) if one is not None else 0.0
+    v = int(got["v_cols"])  # columns of the vocabulary the lead rank's logits cover (all of them unless the head is sharded)
+    lg = got["logits"][:, :, :v]
+    err_oracle = float(np.abs(lg - o_lgs[:, :, :v]).max())
+    err_tp1 = float(np.abs(lg - one["logits"][:, :, :v]).max()) if one is not None else 0.0
     exact = int((got["tf_ids"] == o_ids).sum())
     line = {"run": tag, "max_err_vs_oracle": err_oracle, "max_err_vs_tp1": err_tp1, "argmax_equal": exact,
             "steps": int(o_ids.size), "status": [int(s) for s in got["status"]], "launches": int(got["launches"])}
@@ -92,3 +101,29 @@ def test_tp_matches_tp1_and_oracle(L, O, name, layers, vocab, tmp_path):
         got = run_world(world, spec, tmp_path, "p2p", {"LCU_P2P_SCATTER_RANKS": "2", "LCU_P2P_SCATTER_MIN": "0"}, "_sc")
         assert got["p2p"]
         compare(f"{name} tp{world} p2p scatter", got, o_ids, o_lgs, one, tol, log)
+        # LM head sharded by vocabulary rows: the lead rank picks among the ranks' candidates (ids cover the whole
+        # vocabulary, the logits compared are the lead rank's columns)
+        got = run_world(world, spec_with(spec, tmp_path, head_shard=1), tmp_path, "p2p", {"LCU_P2P_SCATTER_RANKS": "99"}, "_hs")
+        assert got["p2p"] and int(got["v_cols"]) == cfg.vocab // world
+        compare(f"{name} tp{world} p2p push, sharded head", got, o_ids, o_lgs, one, tol, log)
+
+
+def test_bounded_wait_runs_out_and_step_reports_timeout(L, tmp_path):
+    """A rank that stops between two rounds: the other rank's kernels give up after the configured limit, raise bit
+    16 of the status word and RETURN (the context stays usable), and its next lcu_step answers LCU_ERR_TIMEOUT.
+    Two ranks on two GPUs, NVLS off, plain peer stores; nothing faults, traps or hangs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = tmp_path / "timeout.json"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "tests", "tp_timeout_worker.py"), str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    res = json.load(open(out))
+    print("[tp-timeout]", json.dumps(res))
+    assert res["status_before"] == 0
+    assert res["roll_call_error"][0] == -7 and "[1]" in res["roll_call_error"][1]   # host side: learnt before launching
+    assert res["status_after"] & 16                                                 # device side: the wait ran out ...
+    assert res["seconds_for_the_abandoned_round"] < 5.0                             # ... within the limit, and returned
+    assert res["next_step_error"] == -7                                             # LCU_ERR_TIMEOUT
+    assert res["after_reset_status"] == 0

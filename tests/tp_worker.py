@@ -58,6 +58,11 @@ def main():
     o_ids = spec["ids"]
     n = len(prompts)
     ctx = L.load_model(cfg, w, device=local, tp_rank=rank, tp_size=world, comm=comm, max_seqs=max(n, 1))
+    # head_shard 0: the head runs on the lead rank alone and its logits cover the vocabulary; 1: arg-max rounds shard
+    # the head, the lead rank's logits then cover only its own vocab / tp columns
+    head_shard = int(spec.get("head_shard", 0))
+    ctx.set_head_sharding(head_shard)
+    v_cols = cfg.vocab // world if (head_shard and use_p2p and world > 1) else cfg.vocab
     if use_p2p and world > 1:
         def gather(b):
             got = [None] * world
@@ -78,7 +83,7 @@ def main():
             ctx.step([(seqs[i], 0, len(p))], p, out, stream=stream)
             stream.synchronize()
             if rank == 0:
-                logits[i, 0] = ctx.logits(1)[0].float().cpu().numpy()
+                logits[i, 0, :v_cols] = ctx.logits(1).reshape(-1)[:v_cols].float().cpu().numpy()
                 tf_ids[i, 0] = int(out[0, 0].item())
         pos = [len(p) for p in prompts]
         for s in range(steps - 1):
@@ -86,7 +91,7 @@ def main():
             ctx.step(reqs, np.array([o_ids[i][s] for i in range(n)], np.uint32), out, stream=stream)
             stream.synchronize()
             if rank == 0:
-                logits[:, s + 1] = ctx.logits(n).float().cpu().numpy()
+                logits[:, s + 1, :v_cols] = ctx.logits(n).reshape(-1)[:n * v_cols].view(n, v_cols).float().cpu().numpy()
                 tf_ids[:, s + 1] = out[:n, 0].cpu().numpy().view(np.uint32)
             for i in range(n):
                 pos[i] += 1
@@ -123,7 +128,7 @@ def main():
         for s, o in enumerate(keep):
             free_ids[:, s + 1] = o[:n, 0].cpu().numpy().view(np.uint32)
         np.savez(out_path, logits=logits, tf_ids=tf_ids, free_ids=free_ids, launches=launches,
-                 status=np.array([int(t.item()) for t in all_status]), p2p=int(ctx.p2p_enabled))
+                 status=np.array([int(t.item()) for t in all_status]), p2p=int(ctx.p2p_enabled), v_cols=v_cols)
     dist.barrier()
     ctx.close()
     L.check(lib.lcu_comm_destroy(comm))
