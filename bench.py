@@ -219,6 +219,8 @@ class Env:
 
     def connect(self, ctx):
         """Switches a tensor-parallel context to the peer-memory transport (all ranks together)."""
+        if os.environ.get("LCU_BENCH_HEAD_SHARD", "1") == "0":  # A/B switch: head on the lead rank alone
+            ctx.set_head_sharding(0)
         if self.world > 1 and self.use_p2p:
             import torch.distributed as dist
 
@@ -262,7 +264,9 @@ def tp_parity(L, env):
     ids_equal, total, worst = 0, 0, 0.0
 
     # columns of the vocabulary the lead rank's logits cover: all of them, or its own slice when the head is sharded
-    v_cols = cfg.vocab // env.world if (ctx.p2p_enabled and cfg.vocab % env.world == 0 and (cfg.vocab // env.world) % 2 == 0) else cfg.vocab
+    sharded = (ctx.p2p_enabled and os.environ.get("LCU_BENCH_HEAD_SHARD", "1") != "0" and cfg.vocab % env.world == 0
+               and (cfg.vocab // env.world) % 2 == 0)
+    v_cols = cfg.vocab // env.world if sharded else cfg.vocab
 
     def probe(i, s, lg, picked):
         nonlocal ids_equal, total, worst
