@@ -198,7 +198,8 @@ class Env:
         self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         self.dev = f"cuda:{self.local_rank}"
         self.comm = None
-        self.use_p2p = os.environ.get("LCU_BENCH_NCCL", "0") != "1"
+        self.use_p2p = True       # --tp-transport
+        self.head_sharding = True  # --no-head-sharding
 
     def barrier(self):
         import torch
@@ -219,7 +220,7 @@ class Env:
 
     def connect(self, ctx):
         """Switches a tensor-parallel context to the peer-memory transport (all ranks together)."""
-        if os.environ.get("LCU_BENCH_HEAD_SHARD", "1") == "0":  # A/B switch: head on the lead rank alone
+        if not self.head_sharding:  # A/B switch: head on the lead rank alone
             ctx.set_head_sharding(0)
         if self.world > 1 and self.use_p2p:
             import torch.distributed as dist
@@ -264,7 +265,7 @@ def tp_parity(L, env):
     ids_equal, total, worst = 0, 0, 0.0
 
     # columns of the vocabulary the lead rank's logits cover: all of them, or its own slice when the head is sharded
-    sharded = (ctx.p2p_enabled and os.environ.get("LCU_BENCH_HEAD_SHARD", "1") != "0" and cfg.vocab % env.world == 0
+    sharded = (ctx.p2p_enabled and env.head_sharding and cfg.vocab % env.world == 0
                and (cfg.vocab // env.world) % 2 == 0)
     v_cols = cfg.vocab // env.world if sharded else cfg.vocab
 
@@ -328,7 +329,7 @@ def run_decode(L, env, cfg, batch, prompt_range, steps, warmup, want_e2e=True, w
                        max_tokens=max_prefill, max_seqs=max(batch, 1), nctx=nctx)
     del weights
     torch.cuda.empty_cache()
-    # tensor parallelism: all-reduce fused into the projections over NVLink peer memory (LCU_BENCH_NCCL=1: ncclAllReduce)
+    # tensor parallelism: all-reduce fused into the projections over NVLink peer memory (--tp-transport nccl: ncclAllReduce)
     env.connect(ctx)
     res = {"tp_collectives": "peer memory, fused into the projections" if (world > 1 and ctx.p2p_enabled) else
            ("nccl" if world > 1 else "none"), "nctx": nctx}
@@ -466,6 +467,11 @@ def main():
     ap.add_argument("--no-c5", action="store_true", help="N > 1: skip the 70B-shape tensor-parallel record")
     ap.add_argument("--no-tp-parity", action="store_true", help="N > 1: skip the reduced-shape parity check")
     ap.add_argument("--no-ref-kernels", action="store_true", help="skip the reference-kernel baseline record")
+    ap.add_argument("--tp-transport", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: all-reduce over NVLink peer memory fused into the projections (default) or ncclAllReduce")
+    ap.add_argument("--no-head-sharding", action="store_true", help="N > 1: LM head on the lead rank alone, as in the reference")
+    ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                    help="library tuning value (lcu_set_tuning), e.g. pdl_edges=29; for A/B measurements")
     ap.add_argument("--layers", type=int, default=0, metavar="N",
                     help="cut the model to its first N layers: a small case for profiler captures, not a bench line")
     ap.add_argument("--probe-linear", type=int, default=0, metavar="TOKENS",
@@ -478,9 +484,14 @@ def main():
         return 0
     args.warmup = max(args.warmup, 3)
     env = Env()
+    env.use_p2p = args.tp_transport == "p2p"
+    env.head_sharding = not args.no_head_sharding
     rank, world = env.rank, env.world
 
     import llama_cu_b200 as L
+    for kv in args.tune:
+        key, value = kv.split("=", 1)
+        L.set_tuning(key, int(value))
     cname, batch, prange = WORKLOADS[args.workload]
     cfg = L.CONFIGS[cname]
     if args.layers > 0:
@@ -491,6 +502,8 @@ def main():
               "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2 (weights streamed once per step)"}
     if args.layers > 0:
         config["layers"] = cfg.n_layers  # profiling case only
+    if args.tune:
+        config["tuning"] = args.tune
 
     if args.impl == "reference":
         # the reference's own CPU implementation does not exist (it is CUDA-only and its Rust

@@ -177,6 +177,12 @@ LCU_API int lcu_reset_status(lcu_ctx *ctx);
  * up and raises its status bit, in microseconds of SM clock at 2 GHz; default about two seconds.  Applies to every
  * context on the device `ctx` lives on.  (No counterpart in the reference.) */
 LCU_API int lcu_set_wait_limit_us(lcu_ctx *ctx, long long us);
+/* Process-wide tuning values; the defaults are what the committed measurements use.  Keys: "pdl_edges" (bit per
+ * layer edge launched as a programmatic dependent: 0 QKV->attention, 1 attention->O, 2 O->gate|up, 3 gate|up->down,
+ * 4 down->next QKV, 5 last down->LM head; -1 = default), "gemv_ctas_per_sm" (1, 2; read at a shape's first launch),
+ * "q8_rows" (1, 2, 4), "tc" (0: no tcgen05 kernel), "tc_cluster" (0..2), "p2p_scatter_ranks", "p2p_scatter_min".
+ * `ctx` (may be NULL) drops its captured rounds.  A measurement aid without counterpart in the reference. */
+LCU_API int lcu_set_tuning(lcu_ctx *ctx, const char *key, long long value);
 /* Tensor parallelism over peer memory: 1 (default) = arg-max rounds shard the LM head by vocabulary rows — every rank
  * streams vocab / tp rows and sends one candidate pair per request to the lead rank, which keeps the largest value
  * (lowest index among equals, the reference's tie rule); 0 = the head runs on the lead rank alone, as in the reference
@@ -186,16 +192,6 @@ LCU_API int lcu_set_head_sharding(lcu_ctx *ctx, int enabled);
 /* 1 = replay decode rounds from a captured CUDA graph (default), 0 = launch eagerly
  * == the reference's `--no-cuda-graph` switch (xtask/src/main.rs:45-73). */
 LCU_API int lcu_set_cuda_graph(lcu_ctx *ctx, int enabled);
-/* 1 = run decode rounds of up to 4 sequences (single GPU, f16/bf16 weights) as one persistent
- * whole-step kernel, 0 = use the kernel-per-operator path (default).  The reference has no
- * counterpart: it launches one kernel or library call per operator (exec/step.rs:101-138). */
-LCU_API int lcu_set_megakernel(lcu_ctx *ctx, int enabled);
-/* Cycle counters of the persistent kernel (SM clocks spent by CTA 0, summed over the steps since the
- * last call): out16[0..5] tile loops of the QKV / attention / O / gate|up / down / head phases,
- * [8] grid barriers, [9] activation prologues, [10] waits for weight tiles, [11] steps counted.
- * Synchronises the device, copies and clears the counters, then switches counting on or off.
- * (A measurement aid without counterpart in the reference; out16 may be NULL.) */
-LCU_API int lcu_profile_counters(lcu_ctx *ctx, int enable, long long *out16);
 /* Number of kernels of this library launched by the last lcu_step. */
 LCU_API int lcu_last_launch_count(const lcu_ctx *ctx);
 /* Algorithmic HBM bytes of the last round (weights streamed + KV read), for rooflines. */

@@ -99,12 +99,11 @@ _SIGNATURES = {
     "lcu_logits": (C.c_void_p, [C.c_void_p]),
     "lcu_hidden": (C.c_void_p, [C.c_void_p]),
     "lcu_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]),
+    "lcu_set_tuning": (C.c_int, [C.c_void_p, C.c_char_p, C.c_longlong]),
     "lcu_reset_status": (C.c_int, [C.c_void_p]),
     "lcu_set_wait_limit_us": (C.c_int, [C.c_void_p, C.c_longlong]),
     "lcu_set_head_sharding": (C.c_int, [C.c_void_p, C.c_int]),
     "lcu_set_cuda_graph": (C.c_int, [C.c_void_p, C.c_int]),
-    "lcu_set_megakernel": (C.c_int, [C.c_void_p, C.c_int]),
-    "lcu_profile_counters": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_last_launch_count": (C.c_int, [C.c_void_p]),
     "lcu_last_step_bytes": (C.c_double, [C.c_void_p]),
     "lcu_engine_create": (C.c_int, [C.c_void_p, C.c_uint32, C.POINTER(C.c_void_p)]),
@@ -206,6 +205,11 @@ TORCH_DT = None
 def torch_dtype(dt):
     import torch
     return {F16: torch.float16, BF16: torch.bfloat16, F32: torch.float32}[dt]
+
+
+def set_tuning(key, value, ctx=None):
+    """Process-wide tuning value (lcu_set_tuning); `ctx` drops its captured rounds."""
+    check(load_library().lcu_set_tuning(ctx.h if ctx is not None else None, key.encode(), int(value)))
 
 
 def build_sin_cos(nctx, dh, theta):
@@ -348,12 +352,6 @@ class Context:
     def set_cuda_graph(self, enabled):
         check(self.lib.lcu_set_cuda_graph(self.h, int(enabled)))
 
-    def profile_counters(self, enable=True):
-        """Reads and clears the persistent kernel's cycle counters (see lcu_profile_counters)."""
-        out = (C.c_longlong * 16)()
-        check(self.lib.lcu_profile_counters(self.h, int(enable), out))
-        return list(out)
-
     def p2p_connect(self, all_gather_bytes):
         """Switches tensor parallelism from NCCL to NVLink peer memory.  `all_gather_bytes(b)` must return
         the list of every rank's 64-byte `b` in rank order (e.g. built on `torch.distributed.all_gather_object`);
@@ -367,9 +365,6 @@ class Context:
     @property
     def p2p_enabled(self):
         return bool(self.lib.lcu_p2p_enabled(self.h))
-
-    def set_megakernel(self, enabled):
-        check(self.lib.lcu_set_megakernel(self.h, int(enabled)))
 
     @property
     def last_launch_count(self):

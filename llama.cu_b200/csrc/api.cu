@@ -135,7 +135,7 @@ int lcu_op_linear(void *y, int stride_y, const void *x, int stride_x, const void
     const size_t eb = 2;
     const bool batched = n > 4 && gemm_skinny_supported(in, w_dt == LCU_Q8_0) && out % 2 == 0;
     if (batched) gemm_skinny_set_scratch(nullptr, 0, nullptr, 0);  // the stand-alone operator owns no scratch: no K split
-    static const bool tc_on = !(getenv("LCU_TC") && getenv("LCU_TC")[0] == '0');
+    const bool tc_on = tuning().tc != 0;
     const bool tc = batched && tc_on && n > 8 && gemm_tc_supported(in, w_dt == LCU_Q8_0);
     if (tc) gemm_tc_set_scratch(nullptr, 0, nullptr, 0, nullptr);
     for (int t0 = 0; t0 < n;) {

@@ -31,6 +31,18 @@ int cuda_fail(cudaError_t e, const char *what);
     } while (0)
 
 inline cudaStream_t as_stream(lcu_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Process-wide tuning values (lcu_set_tuning); the defaults are what the committed measurements use.
+struct Tuning {
+    int pdl_edges = -1;            // bit per layer edge launched as a programmatic dependent; -1: 28 (GEMV rounds) / 30 (batched)
+    int gemv_ctas_per_sm = 2;      // GEMV CTAs per SM (read at a shape's first launch)
+    int q8_rows = 4;               // Q8_0 GEMV: row pairs per thread
+    int tc = 1;                    // 0: keep the tcgen05 kernel out (mma.sync kernel for every batched round)
+    int tc_cluster = 1;            // cluster split-K form of the tcgen05 kernel: 0 never, 1 where it measured faster, 2 wherever it applies
+    int p2p_scatter_ranks = 99;    // ranks from which the peer all-reduce takes the reduce-scatter + all-gather form
+    long p2p_scatter_min = 131072; // ... for rounds of at least this many bytes
+};
+Tuning &tuning();
 int sm_count();  // SMs of the current device (cached per device)
 
 // ------------------------------------------------------------------ scalar types

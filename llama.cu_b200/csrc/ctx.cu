@@ -7,12 +7,12 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "attention.cuh"
 #include "common.cuh"
 #include "gemv.cuh"
-#include "megakernel.cuh"
 #include "ops.cuh"
 #include "p2p.cuh"
 #include "sample.cuh"
@@ -46,6 +46,11 @@ int sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
     cache[dev] = n;
     return n;
+}
+
+Tuning &tuning() {
+    static Tuning t;
+    return t;
 }
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -115,20 +120,6 @@ struct lcu_ctx {
     bool desc_used[RING] = {false, false, false, false};
     int ring_idx = 0;
 
-    // persistent whole-step kernel (1..4 sequences, single GPU, f16/bf16 weights)
-    bool use_megakernel = false;  // opt-in (lcu_set_megakernel): not yet faster than the kernel-per-operator path
-    bool mk_ok[3] = {false, false, false};   // for 1, 2, 4 tokens
-    size_t mk_smem[3] = {0, 0, 0};
-    int mk_stages[3] = {0, 0, 0}, mk_xbytes[3] = {0, 0, 0}, mk_pbytes[3] = {0, 0, 0};
-    MkPhase *mk_phases_dev = nullptr;
-    int mk_n_phases = 0;
-    bool mk_phases_valid = false;
-    float *mk_attn_part = nullptr, *mk_best_v = nullptr;
-    uint32_t *mk_best_i = nullptr;
-    unsigned *mk_grid_bar = nullptr;
-    long long *mk_prof = nullptr;
-    bool mk_profile = false;
-
     // tensor parallelism over peer memory (set up by lcu_p2p_create / lcu_p2p_attach)
     P2pState p2p;
 
@@ -169,13 +160,11 @@ static DescLayout desc_layout(int n_tok, int n_req, int pt_stride) {
 // with a shorter context simply uses fewer of its CTAs.  Fixed per round shape so that a captured graph
 // stays valid as contexts grow.  Rounds with enough tokens to fill the GPU on their own (prefill) are
 // not split.
-static int batched_min_tokens();
+// Fewest tokens in a round for which the linear layers run as batched tensor-core kernels instead of
+// the register-blocked GEMV (measured on the 8B shapes: the GEMV wins up to 2 tokens).
+static int batched_min_tokens() { return 3; }
 
 static void attn_plan(const lcu_ctx *c, int n_tok, int *n_splits, int *tps) {
-    static const int env_tps = [] {
-        const char *e = getenv("LCU_ATTN_TPS");
-        return e ? atoi(e) : 0;
-    }();
     const int ctas = c->nkvh_l * n_tok;
     const int max_tiles = (c->desc.nctx + 63) / 64;
     if (ctas >= 8 * sm_count() || max_tiles <= 1) {
@@ -187,11 +176,9 @@ static void attn_plan(const lcu_ctx *c, int n_tok, int *n_splits, int *tps) {
     int t = (int)(((long)ctas * max_tiles + 4L * sm_count() - 1) / (4L * sm_count()));
     if (t > 4) t = 4;
     if (t < 1) t = 1;
-    if (env_tps > 0) t = env_tps;
     // a round of a few tokens merges its splits inside one thread-block cluster (at most 8 CTAs): take 2 tiles per
     // CTA when that is what it needs
-    static const int small_cluster = getenv("LCU_ATTN_CLUSTER") ? atoi(getenv("LCU_ATTN_CLUSTER")) : 1;
-    if (small_cluster && env_tps <= 0 && n_tok < batched_min_tokens() && t == 1 && max_tiles > 8 && max_tiles <= 16) t = 2;
+    if (n_tok < batched_min_tokens() && t == 1 && max_tiles > 8 && max_tiles <= 16) t = 2;
     int z = (max_tiles + t - 1) / t;
     int z_cap = 2048 / n_tok;  // bounds the partial-output scratch
     if (z_cap > 64) z_cap = 64;
@@ -208,17 +195,6 @@ static int attn_splits(const lcu_ctx *c, int n_tok) {
     int z, t;
     attn_plan(c, n_tok, &z, &t);
     return z;
-}
-
-// Fewest tokens in a round for which the linear layers run as batched tensor-core kernels instead of
-// the register-blocked GEMV (measured on the 8B shapes: the GEMV wins up to 2 tokens).
-static int batched_min_tokens() {
-    static const int v = [] {
-        const char *e = getenv("LCU_BATCHED_MIN");
-        int x = e ? atoi(e) : 3;
-        return x < 1 ? 1 : x;
-    }();
-    return v;
 }
 
 // Rows of the LM head one rank holds when the head is sharded by vocabulary (0: the shape does not allow it).
@@ -248,7 +224,6 @@ static bool is_linear_kind(int kind) {
 
 // captured graphs hold weight pointers: any change of registered memory drops them
 static void drop_graphs(lcu_ctx *c) {
-    c->mk_phases_valid = false;
     for (auto &g : c->graphs)
         if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     c->graphs.clear();
@@ -377,13 +352,9 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     size_t sz_pairs = align256((size_t)c->max_tokens * sizeof(lcu_kv_pair));
     size_t sz_head_local = align256((size_t)c->max_seqs * sizeof(lcu_kv_pair));
     c->desc_cap = align256(desc_layout(c->max_tokens, c->max_seqs, c->pt_stride).total);
-    const int grid = sm_count();
-    size_t sz_mk_part = align256((size_t)4 * c->nh_l * 16 * (d.dh + 2) * 4);
-    size_t sz_mk_best = align256((size_t)grid * 4 * 4);
-    size_t sz_mk_phases = align256((size_t)(d.n_layers * 5 + 1) * sizeof(MkPhase));
     const size_t sz_sk_ws = (size_t)16 << 20, sz_sk_tickets = (size_t)16 << 10;
     size_t total = sz_x + 2 * sz_q + sz_act + sz_logits + sz_attn + c->sample_ws_bytes + sz_pairs + 512 + c->desc_cap +
-                   sz_mk_part + 2 * sz_mk_best + sz_mk_phases + sz_x + sz_sk_ws + sz_sk_tickets + sz_head_local;
+                   sz_x + sz_sk_ws + sz_sk_tickets + sz_head_local;
     cudaError_t e = cudaMalloc(&c->arena, total);
     if (e != cudaSuccess) {
         delete c;
@@ -400,14 +371,8 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
     c->sample_ws = p; p += c->sample_ws_bytes;
     c->pre_pairs = reinterpret_cast<lcu_kv_pair *>(p); p += sz_pairs;
     c->dev_status = reinterpret_cast<uint32_t *>(p);
-    c->mk_grid_bar = reinterpret_cast<unsigned *>(p + 128);
-    c->mk_prof = reinterpret_cast<long long *>(p + 256);
     p += 512;
     c->desc_dev = p; p += c->desc_cap;
-    c->mk_attn_part = reinterpret_cast<float *>(p); p += sz_mk_part;
-    c->mk_best_v = reinterpret_cast<float *>(p); p += sz_mk_best;
-    c->mk_best_i = reinterpret_cast<uint32_t *>(p); p += sz_mk_best;
-    c->mk_phases_dev = reinterpret_cast<MkPhase *>(p); p += sz_mk_phases;
     c->hbuf = p; p += sz_x;
     c->sk_ws = p; p += sz_sk_ws;
     c->sk_tickets = reinterpret_cast<unsigned *>(p); p += sz_sk_tickets;
@@ -449,19 +414,6 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
                 lcu_ctx_destroy(c);
                 return rc;
             }
-        }
-        // the persistent whole-step kernel: single GPU, unquantised weights, shapes it can tile
-        int R, KC, nkc;
-        bool tiles_ok = !q8 && tp_size == 1 && mk_plan_tiles(d.d, &R, &KC, &nkc) && mk_plan_tiles(c->qd, &R, &KC, &nkc) &&
-                        mk_plan_tiles(c->di_l, &R, &KC, &nkc) && d.vocab % 2 == 0;
-        int max_in = d.d > c->qd ? d.d : c->qd;
-        if (c->di_l > max_in) max_in = c->di_l;
-        for (int i = 0; i < 3 && tiles_ok; ++i) {
-            int nt = 1 << i;
-            if (nt > c->max_seqs && i > 0) break;
-            c->mk_smem[i] = mk_smem_bytes(nt, max_in, c->nh_l, c->nkvh_l, d.dh, &c->mk_stages[i], &c->mk_xbytes[i], &c->mk_pbytes[i]);
-            if (!c->mk_smem[i] || nt * c->nkvh_l > sm_count()) continue;
-            c->mk_ok[i] = mk_prepare(c->dt, nt, c->mk_smem[i]) == LCU_OK;
         }
     }
     *out = c;
@@ -634,20 +586,22 @@ int lcu_set_cuda_graph(lcu_ctx *c, int enabled) {
     c->use_graph = enabled != 0;
     return LCU_OK;
 }
-int lcu_set_megakernel(lcu_ctx *c, int enabled) {
-    LCU_REQUIRE(c, "set_megakernel: null context");
-    c->use_megakernel = enabled != 0;
-    return LCU_OK;
-}
-int lcu_profile_counters(lcu_ctx *c, int enable, long long *out16) {
-    LCU_REQUIRE(c, "profile_counters: null context");
-    LCU_CHECK_CUDA(cudaDeviceSynchronize());
-    if (out16) LCU_CHECK_CUDA(cudaMemcpy(out16, c->mk_prof, 16 * sizeof(long long), cudaMemcpyDeviceToHost));
-    LCU_CHECK_CUDA(cudaMemset(c->mk_prof, 0, 16 * sizeof(long long)));
-    if (c->mk_profile != (enable != 0)) {
-        c->mk_profile = enable != 0;
-        drop_graphs(c);
+int lcu_set_tuning(lcu_ctx *c, const char *key, long long value) {
+    LCU_REQUIRE(key, "set_tuning: null key");
+    Tuning &t = tuning();
+    const std::string k(key);
+    if (k == "pdl_edges") t.pdl_edges = (int)value;
+    else if (k == "gemv_ctas_per_sm") { LCU_REQUIRE(value >= 1 && value <= 2, "set_tuning: gemv_ctas_per_sm = %lld (1, 2)", value); t.gemv_ctas_per_sm = (int)value; }
+    else if (k == "q8_rows") { LCU_REQUIRE(value == 1 || value == 2 || value == 4, "set_tuning: q8_rows = %lld (1, 2, 4)", value); t.q8_rows = (int)value; }
+    else if (k == "tc") t.tc = value != 0;
+    else if (k == "tc_cluster") { LCU_REQUIRE(value >= 0 && value <= 2, "set_tuning: tc_cluster = %lld (0..2)", value); t.tc_cluster = (int)value; }
+    else if (k == "p2p_scatter_ranks") t.p2p_scatter_ranks = (int)value;
+    else if (k == "p2p_scatter_min") t.p2p_scatter_min = (long)value;
+    else {
+        set_error("set_tuning: unknown key '%s'", key);
+        return LCU_ERR_INVALID;
     }
+    if (c) drop_graphs(c);  // captured rounds hold the old choice
     return LCU_OK;
 }
 int lcu_set_head_sharding(lcu_ctx *c, int enabled) {
@@ -688,34 +642,6 @@ int lcu_device_status(lcu_ctx *c, lcu_stream_t stream, uint32_t *status_out) {
 
 namespace {
 
-// (Re)builds the device-side phase list of the persistent kernel from the registered weights.
-int mk_build_phases(lcu_ctx *c) {
-    if (c->mk_phases_valid) return LCU_OK;
-    const lcu_model_desc &d = c->desc;
-    std::vector<MkPhase> ph;
-    auto weight_phase = [&](int kind, int layer, const void *w, const void *norm, int in, int out, int swiglu_di) {
-        MkPhase p{};
-        p.w = w; p.norm_w = norm; p.kind = kind; p.layer = layer; p.in = in; p.n_pairs = out / 2; p.swiglu_di = swiglu_di;
-        mk_plan_tiles(in, &p.R, &p.KC, &p.n_kc);
-        ph.push_back(p);
-    };
-    for (int l = 0; l < d.n_layers; ++l) {
-        const LayerWeights &W = c->layers[l];
-        weight_phase(MK_QKV, l, W.qkv, W.attn_norm, d.d, c->qd + 2 * c->kvd, 0);
-        MkPhase at{};
-        at.kind = MK_ATTN; at.layer = l;
-        ph.push_back(at);
-        weight_phase(MK_O, l, W.o, nullptr, c->qd, d.d, 0);
-        weight_phase(MK_GATE_UP, l, W.gate_up, W.ffn_norm, d.d, 2 * c->di_l, c->di_l);
-        weight_phase(MK_DOWN, l, W.down, nullptr, c->di_l, d.d, 0);
-    }
-    weight_phase(MK_HEAD, d.n_layers, c->lm_head, c->out_norm, d.d, d.vocab, 0);
-    LCU_CHECK_CUDA(cudaMemcpy(c->mk_phases_dev, ph.data(), ph.size() * sizeof(MkPhase), cudaMemcpyHostToDevice));
-    c->mk_n_phases = (int)ph.size();
-    c->mk_phases_valid = true;
-    return LCU_OK;
-}
-
 struct Round {
     int n_tok, n_req, n_fast;
     bool any_sampling;
@@ -727,15 +653,14 @@ struct Round {
 int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t s, int *count) {
     const lcu_model_desc &d = c->desc;
     const int dt = c->dt;
-    // Programmatic dependent launch is used edge by edge (pdl_edges below); putting the attribute on EVERY launch
-    // measured slower than plain graph edges (3.8 ms vs 3.3 ms per 8B step) and stays off unless LCU_PDL=1.
-    static const bool pdl = getenv("LCU_PDL") && getenv("LCU_PDL")[0] == '1';
-    static const int pdl_trigger = getenv("LCU_PDL_TRIGGER") ? atoi(getenv("LCU_PDL_TRIGGER")) : 2;
-    // programmatic dependent launch on selected edges of a layer only (bit 0: QKV -> attention, 1: attention -> O,
-    // 2: O -> gate|up, 3: gate|up -> down, 4: down -> next QKV): the successor is launched with the attribute and the
-    // predecessor releases it as soon as all its CTAs are running
-    static const int pdl_edges_env = getenv("LCU_PDL_EDGES") ? atoi(getenv("LCU_PDL_EDGES")) : -1;
-    static const int early_prefetch = getenv("LCU_PREFETCH") ? atoi(getenv("LCU_PREFETCH")) : 1;
+    // Programmatic dependent launch, edge by edge (bit 0: QKV -> attention, 1: attention -> O, 2: O -> gate|up,
+    // 3: gate|up -> down, 4: down -> next QKV, 5: last down -> LM head): the successor is launched with the attribute
+    // and the predecessor releases it as soon as all its CTAs are running.  Putting the attribute on EVERY launch
+    // measured slower than plain graph edges (3.8 ms against 3.3 ms per 8B step) and is not offered.
+    const bool pdl = false;
+    const int pdl_trigger = 2;     // a kernel without a dependent edge releases nothing before it exits
+    const int pdl_edges_env = tuning().pdl_edges;
+    const int early_prefetch = 1;  // GEMV request order: activations, then weights (weights first when launched early)
     int launches = 0;
     unsigned char *D = c->desc_dev;
     uint32_t *tokens = reinterpret_cast<uint32_t *>(D + r.L.tokens);
@@ -784,21 +709,21 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     const int pdl_edges = pdl_edges_env >= 0 ? pdl_edges_env : (batched ? 30 : 28);
     gemm_skinny_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096);
     gemm_tc_set_scratch(c->sk_ws, c->sk_ws_bytes, c->sk_tickets, 4096, c->dev_status);
-    static const bool tc_on = !(getenv("LCU_TC") && getenv("LCU_TC")[0] == '0');
+    const bool tc_on = tuning().tc != 0;
     const int norm_dt = d.norm_dtype;
     // One linear layer over `n` rows: token groups of <= 4 through the GEMV (RMSNorm fused as its
     // prologue), or blocks of <= 64 through the tensor-core kernel (activations normalised before).
     const bool p2p = c->tp_size > 1 && c->p2p.ready;
-    // large rounds reduce-scatter + all-gather through the column owners instead of pushing everything to everyone
-    static const long scatter_min = getenv("LCU_P2P_SCATTER_MIN") ? atol(getenv("LCU_P2P_SCATTER_MIN")) : 131072;
-    // (from 4 ranks on: with 2 ranks both forms move the same bytes and the scatter form only adds a hop —
-    // measured 5.5 ms against 4.9 ms per 8B batch-32 step)
-    // Off unless asked for (LCU_P2P_SCATTER_RANKS=4 is the intended setting): validated with 2 ranks only so far.
-    static const int scatter_ranks = getenv("LCU_P2P_SCATTER_RANKS") ? atoi(getenv("LCU_P2P_SCATTER_RANKS")) : 99;
+    // large rounds may reduce-scatter + all-gather through the column owners instead of pushing everything to everyone
+    // (tuning: p2p_scatter_ranks / p2p_scatter_min; off by default — measured on the 70B shape, 64 tokens per round:
+    // 16.9 ms per step with the push form against 17.5 ms with this one on 4 ranks; with 2 ranks both forms move the
+    // same bytes and this one only adds a hop)
+    const long scatter_min = tuning().p2p_scatter_min;
+    const int scatter_ranks = tuning().p2p_scatter_ranks;
     const int scatter_cols = (p2p && c->tp_size >= scatter_ranks && (long)r.n_tok * d.d * 2 >= scatter_min &&
                               d.d % (c->tp_size * 8) == 0) ? d.d / c->tp_size : 0;
     c->p2p.parity = 0;  // every step holds an even number of all-reduces, so captured graphs agree on it
-    static const bool reduce_pdl = !(getenv("LCU_P2P_REDUCE_PDL") && getenv("LCU_P2P_REDUCE_PDL")[0] == '0');
+    const bool reduce_pdl = true;  // the reduction kernel is a programmatic dependent of the producing projection
     int linear_ctas = 0;  // CTAs of the launches of the last `linear` call
     auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
                       const void *norm_w, bool push = false, int edge_in = -1, int edge_out = -1) -> int {
@@ -882,8 +807,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             // GEMV rounds: the splits of a (token, KV head) merge through distributed shared memory (one cluster of up
             // to 8 CTAs) instead of scratch + ticket: 2.89 -> 2.83 ms per 8B batch-1 step.  Batched rounds keep the
             // scratch merge (many CTAs without work would sit in cluster barriers: 4.77 -> 5.75 ms at batch 32).
-            static const int attn_cluster = getenv("LCU_ATTN_CLUSTER") ? atoi(getenv("LCU_ATTN_CLUSTER")) : 1;
-            a.cluster_z = (attn_cluster && !batched && n_splits >= 2 && n_splits <= 8) ? n_splits : 0;
+            a.cluster_z = (!batched && n_splits >= 2 && n_splits <= 8) ? n_splits : 0;
             // launched as a programmatic dependent of the QKV projection (edge 0, off by default: it measured no
             // gain, the GEMV's CTAs fill every register file until they leave) a decode round fetches the cached
             // rows of earlier rounds before it waits; its own dependents start once its first tile has landed
@@ -983,62 +907,6 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             if (rc) return rc;
             ++launches;
         }
-    }
-    *count = launches;
-    return LCU_OK;
-}
-
-// One decode round (1..4 sequences, one token each) as ONE persistent cooperative kernel.
-int enqueue_round_mk(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t s, int *count) {
-    const lcu_model_desc &d = c->desc;
-    const int vi = r.n_tok <= 1 ? 0 : (r.n_tok == 2 ? 1 : 2);
-    unsigned char *D = c->desc_dev;
-    MkArgs a{};
-    a.phases = c->mk_phases_dev;
-    a.n_phases = c->mk_n_phases;
-    a.n_tok = r.n_tok;
-    a.d = d.d; a.qd = c->qd; a.kvd = c->kvd; a.dh = d.dh; a.nh = c->nh_l; a.nkvh = c->nkvh_l; a.di = c->di_l; a.vocab = d.vocab;
-    a.eps = d.eps;
-    a.norm_f32 = d.norm_dtype == LCU_F32;
-    a.tokens = reinterpret_cast<uint32_t *>(D + r.L.tokens);
-    a.pos = reinterpret_cast<const uint32_t *>(D + r.L.pos);
-    a.fast_map = reinterpret_cast<const uint32_t *>(D + r.L.fast_map);
-    a.n_fast = r.n_fast;
-    a.pre_pairs_in = c->pre_pairs;
-    a.page_table = reinterpret_cast<const int32_t *>(D + r.L.page_table);
-    a.pt_stride = c->pt_stride;
-    a.embd = c->embd;
-    a.sin_t = c->sin_t; a.cos_t = c->cos_t;
-    a.kv_pool = c->pool;
-    a.geom = c->geom;
-    a.x = c->x; a.q = c->q; a.act = c->act; a.logits = c->logits;
-    a.attn_part = c->mk_attn_part;
-    a.s_max = mk_splits(sm_count(), r.n_tok <= 1 ? 1 : (r.n_tok == 2 ? 2 : 4), c->nkvh_l);
-    a.head_best_v = c->mk_best_v;
-    a.head_best_i = c->mk_best_i;
-    a.out = out_dev;
-    a.out_copy = c->pre_pairs;
-    a.grid_bar = c->mk_grid_bar;
-    a.status = c->dev_status;
-    a.prof = c->mk_profile ? c->mk_prof : nullptr;
-    a.n_stages = c->mk_stages[vi];
-    {
-        static const int l2_ahead = getenv("LCU_MK_L2_AHEAD") ? atoi(getenv("LCU_MK_L2_AHEAD")) : 0;
-        a.l2_ahead = l2_ahead;
-    }
-    a.smem_x_bytes = c->mk_xbytes[vi];
-    a.smem_part_bytes = c->mk_pbytes[vi];
-    LCU_CHECK_CUDA(cudaMemsetAsync(c->mk_grid_bar, 0, sizeof(unsigned), s));
-    int rc = mk_launch(a, c->dt, c->mk_smem[vi], s);
-    if (rc) return rc;
-    int launches = 1;
-    if (r.any_sampling) {  // rows that sample are redone from the logits; arg-max rows keep their pair
-        const lcu_sample_args *args = reinterpret_cast<const lcu_sample_args *>(D + r.L.args);
-        const float *randoms = reinterpret_cast<const float *>(D + r.L.randoms);
-        rc = sample_rows(out_dev, c->pre_pairs, c->logits, r.n_req, (size_t)d.vocab, args, randoms, c->dt, c->sample_ws,
-                         c->sample_ws_bytes, s, false, true);
-        if (rc) return rc;
-        launches += 3;
     }
     *count = launches;
     return LCU_OK;
@@ -1215,27 +1083,21 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
 
     // decode rounds replay a captured graph; everything else (and stream 0) runs eagerly.
     // NCCL collectives are captured like any other node (exec/step.rs:82-86).
-    const int mk_vi = n_tok <= 1 ? 0 : (n_tok == 2 ? 1 : 2);
-    const bool use_mk = c->use_megakernel && decode_only && n_tok <= 4 && c->tp_size == 1 && c->mk_ok[mk_vi];
-    if (use_mk) {
-        rc = mk_build_phases(c);
-        if (rc) return rc;
-    }
     bool graph_ok = c->use_graph && decode_only && s != nullptr;
     if (!graph_ok) {
         int count = 0;
-        rc = use_mk ? enqueue_round_mk(c, r, out_dev, s, &count) : enqueue_round(c, r, out_dev, s, &count);
+        rc = enqueue_round(c, r, out_dev, s, &count);
         c->last_launches = count;
         return rc;
     }
     std::vector<int> key = {n_req, n_tok, n_fast, any_sampling ? 1 : 0, (int)((uintptr_t)out_dev & 0x7fffffff),
-                            (int)((uintptr_t)out_dev >> 31), use_mk ? 1 : 0, c->head_shard ? 1 : 0};
+                            (int)((uintptr_t)out_dev >> 31), c->head_shard ? 1 : 0};
     auto it = c->graphs.find(key);
     if (it == c->graphs.end()) {
         cudaGraph_t graph = nullptr;
         LCU_CHECK_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         int count = 0;
-        rc = use_mk ? enqueue_round_mk(c, r, out_dev, s, &count) : enqueue_round(c, r, out_dev, s, &count);
+        rc = enqueue_round(c, r, out_dev, s, &count);
         cudaError_t e = cudaStreamEndCapture(s, &graph);
         if (rc) {
             if (graph) cudaGraphDestroy(graph);

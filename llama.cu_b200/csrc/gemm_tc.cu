@@ -653,198 +653,6 @@ gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, con
     }
 }
 
-// ------------------------------------------------------------------ tokens-on-M form
-// D[128 token lanes x BN weight rows] += X[128 x 64] . W_tile[BN x 64]^T: the token block (<= 64 real rows, the
-// rest of the 128-row operand is never read back) is the M side and a tile of BN weight rows the N side.  BN is
-// a free multiple of 16, so the row dimension of ANY matrix of the model cuts into enough equal tiles to keep
-// all SMs busy (no K splitting, no partial sums through scratch), and a TMEM lane holds consecutive outputs
-// of ONE token: the epilogue goes straight from tcgen05.ld registers to 16-byte stores.
-//   SwiGLU tiles hold BN/2 gate rows followed by their BN/2 up rows (two TMA boxes).
-// Measured result: correct, but slower than the row-block form for the tile heights that balance the 8B
-// shapes (BN = 32..48): every MMA re-reads the whole 128-row activation operand from shared memory (4 KB per
-// K = 16 step although at most 64 rows are real), i.e. about 5 bytes of shared-memory reads per weight byte
-// at BN = 32, and the kernel becomes shared-memory-bandwidth bound (8B batch-32 step 7.4 ms against 5.2 ms).
-// It is kept behind LCU_TC_LAYOUT=tokens; an M = 64 variant would halve that overhead.
-constexpr int TCN_A_BYTES = 128 * TC_BK * 2;  // activation operand region of a stage (128 rows x 128 bytes)
-
-template <class T>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tcn_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                int n_tiles, int Nbox, int BN, int n_stages, int tm_cols, uint32_t idesc, uint32_t *status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
-    const int stage_bytes = TCN_A_BYTES + BN * 128;
-    TcShared *sh = reinterpret_cast<TcShared *>(smem + (size_t)n_stages * stage_bytes);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nkb = a.in / TC_BK;
-    const bool swiglu = a.epilogue == EPI_SWIGLU;
-    const int BP = BN / 2;  // SwiGLU: pairs per tile
-
-    if (tid == 0) {
-        for (int i = 0; i < n_stages; ++i) {
-            tc_mbar_init(tc_smem(&sh->full[i]), 1);
-            tc_mbar_init(tc_smem(&sh->empty[i]), 1);
-        }
-        for (int i = 0; i < 2; ++i) {
-            tc_mbar_init(tc_smem(&sh->tmem_full[i]), 1);
-            tc_mbar_init(tc_smem(&sh->tmem_empty[i]), 1);
-        }
-        sh->abort_flag = 0;
-        sh->last = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // rows of the activation operand that no TMA box ever fills: keep them zero (their products are never read)
-    for (int st = 0; st < n_stages; ++st) {
-        uint4 *p = reinterpret_cast<uint4 *>(smem + (size_t)st * stage_bytes + (size_t)Nbox * 128);
-        for (int i = tid; i < (128 - Nbox) * 8; i += TC_THREADS) p[i] = make_uint4(0, 0, 0, 0);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(&sh->tmem_base)), "r"(tm_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = sh->tmem_base;
-
-    if (warp == 0 && lane == 0) {
-        // ---------------- TMA producer
-        grid_dep_wait();
-        int it = 0;
-        const uint32_t tx = (uint32_t)(Nbox * 128 + BN * 128);
-        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x) {
-            const int row_a = swiglu ? tile * BP : tile * BN;
-            const int row_b = a.di + tile * BP;  // SwiGLU only
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-                const int slot = it % n_stages;
-                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
-                if (!tc_mbar_wait(tc_smem(&sh->empty[slot]), parity ^ 1u, &sh->abort_flag)) {
-                    atomicOr(status, 4u);
-                    sh->abort_flag = 1;
-                    break;
-                }
-                const uint32_t bar = tc_smem(&sh->full[slot]);
-                const uint32_t dst = tc_smem(smem + (size_t)slot * stage_bytes);
-                tc_mbar_expect_tx(bar, tx);
-                const int kx = kb * TC_BK;
-                tc_tma_2d(dst, &map_x, kx, 0, bar);
-                tc_tma_2d(dst + TCN_A_BYTES, &map_w, kx, row_a, bar);
-                if (swiglu) tc_tma_2d(dst + TCN_A_BYTES + BP * 128, &map_w, kx, row_b, bar);
-            }
-        }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer
-        int it = 0, ti = 0;
-        for (int tile = blockIdx.x; tile < n_tiles && !sh->abort_flag; tile += gridDim.x, ++ti) {
-            const int ab = ti & 1;
-            if (!tc_mbar_wait(tc_smem(&sh->tmem_empty[ab]), ((uint32_t)(ti >> 1) & 1u) ^ 1u, &sh->abort_flag)) {
-                atomicOr(status, 4u);
-                sh->abort_flag = 1;
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t d_tmem = tmem + (uint32_t)(ab * (tm_cols / 2));
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-                const int slot = it % n_stages;
-                const uint32_t parity = (uint32_t)(it / n_stages) & 1u;
-                if (!tc_mbar_wait(tc_smem(&sh->full[slot]), parity, &sh->abort_flag)) {
-                    atomicOr(status, 4u);
-                    sh->abort_flag = 1;
-                    break;
-                }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = tc_smem(smem + (size_t)slot * stage_bytes), sb = sa + TCN_A_BYTES;
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)
-                    tc_mma_f16(d_tmem, tc_desc(sa + k * 32), tc_desc(sb + k * 32), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                tc_commit(tc_smem(&sh->empty[slot]));
-            }
-            tc_commit(tc_smem(&sh->tmem_full[ab]));
-        }
-    } else if (warp >= 2) {
-        // ---------------- epilogue warps: lane = token, columns = consecutive outputs of that token
-        const int et = tid - 64;
-        const int q = warp & 3;  // a warp may only touch TMEM lanes [32q, 32q + 32)
-        const int n = q * 32 + lane;
-        const bool warp_active = q * 32 < a.n_tok;
-        const bool tok = n < a.n_tok;
-        int ti = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++ti) {
-            const int ab = ti & 1;
-            bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[ab]), (uint32_t)(ti >> 1) & 1u, &sh->abort_flag);
-            if (!ok) {
-                atomicOr(status, 4u);
-                sh->abort_flag = 1;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ok && warp_active) {
-                const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * (tm_cols / 2));
-                if (swiglu) {
-                    for (int c0 = 0; c0 < BP; c0 += 8) {
-                        uint32_t g[8], up[8];
-                        tc_ld8(tbase + (uint32_t)c0, g);
-                        tc_ld8(tbase + (uint32_t)(BP + c0), up);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        const int first = tile * BP + c0;
-                        if (tok && first + 8 <= a.di) {
-                            float v[8], u[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                v[i] = __uint_as_float(g[i]);
-                                u[i] = __uint_as_float(up[i]);
-                            }
-                            TcPre pre;
-                            tc_finish<T>(a, n, first, v, u, pre);
-                        }
-                    }
-                } else {
-                    for (int c0 = 0; c0 < BN; c0 += 16) {
-                        uint32_t r[16];
-                        tc_ld16(tbase + (uint32_t)c0, r);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        const int first = tile * BN + c0;
-                        TcPre pre[2];
-                        const bool v0 = tok && first + 8 <= a.out, v1 = tok && first + 16 <= a.out;
-                        if (v0) tc_prefetch<T>(a, n, first, pre[0]);
-                        if (v1) tc_prefetch<T>(a, n, first + 8, pre[1]);
-                        float v[8], u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                        if (v0) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-                            tc_finish<T>(a, n, first, v, u, pre[0]);
-                        }
-                        if (v1) {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 + i]);
-                            tc_finish<T>(a, n, first + 8, v, u, pre[1]);
-                        }
-                    }
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            // the barrier also ANDs every thread's `ok`: the 128 epilogue threads leave the loop together or not at
-            // all (a thread whose wait ran out must not strand the others at the next barrier)
-            uint32_t all_ok;
-            asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 p, %1, 0;\n bar.red.and.pred q, 2, 128, p;\n selp.u32 %0, 1, 0, q;\n}"
-                         : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
-            if (et == 0) {  // the accumulator may be overwritten from here on
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&sh->tmem_empty[ab])) : "memory");
-            }
-            if (!all_ok) break;
-        }
-    }
-    // ---------------- tail
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    p2p_signal(a.push);  // no-op without tensor parallelism
-    __syncthreads();
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tm_cols) : "memory");
-    }
-}
-
 // ------------------------------------------------------------------ host side
 
 typedef CUresult (*TcEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -930,7 +738,6 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         auto it = done.find(dev);
         if (it == done.end()) {
             LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-            LCU_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             LCU_CHECK_CUDA(cudaFuncSetAttribute(gemm_tck_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
             void *p = nullptr;
             LCU_CHECK_CUDA(cudaGetSymbolAddress(&p, g_tc_fallback_status));
@@ -951,47 +758,6 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         vec_ok = vec_ok && a.dh % 8 == 0 && a.qd % 8 == 0 && a.kvd % 8 == 0 && ((uintptr_t)a.kv_pool % 16) == 0 &&
                  ((uintptr_t)a.sin_t % 16) == 0 && ((uintptr_t)a.cos_t % 16) == 0;
     const int vec = vec_ok ? 1 : 0;
-    // opt-in (LCU_TC_LAYOUT=tokens): measured slower than the row-block form on the 8B shapes, see the kernel's header
-    static const bool tokens_on_m = getenv("LCU_TC_LAYOUT") && getenv("LCU_TC_LAYOUT")[0] == 't';
-    if (vec && tokens_on_m) {
-        // ---- tokens on M: pick the tile height BN (weight rows, a multiple of 16) that finishes soonest when the
-        // tiles are dealt round-robin to the SMs: rounds x BN, larger BN on ties (fewer activation re-reads)
-        static const int env_bn = getenv("LCU_TC_BN") ? atoi(getenv("LCU_TC_BN")) : 0;
-        const bool swiglu = a.epilogue == EPI_SWIGLU;
-        const int rows = swiglu ? a.di : a.out;  // rows (pairs for SwiGLU) to cover; a SwiGLU tile of BN holds BN/2 pairs
-        int best_bn = 0;
-        long best_cost = -1;
-        for (int bn = 32; bn <= 128; bn += 16) {
-            if (env_bn) bn = env_bn;
-            const int per = swiglu ? bn / 2 : bn;
-            const int tiles = (rows + per - 1) / per;
-            const long cost = (long)((tiles + sms - 1) / sms) * bn;
-            if (best_cost < 0 || cost <= best_cost) {
-                best_cost = cost;
-                best_bn = bn;
-            }
-            if (env_bn) break;
-        }
-        const int BN = best_bn, per = swiglu ? BN / 2 : BN;
-        LCU_REQUIRE(BN >= 16 && BN <= 128 && BN % 16 == 0, "gemm_tc: tile height %d", BN);
-        const int n_tiles = (rows + per - 1) / per;
-        const int stage_bytes = TCN_A_BYTES + BN * 128;
-        int stages = (int)(((size_t)227 * 1024 - 1024 - sizeof(TcShared) - 64) / stage_bytes);
-        if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
-        const size_t smem_n = 1024 + (size_t)stages * stage_bytes + sizeof(TcShared) + 64;
-        int tm_cols = 32;
-        while (tm_cols < 2 * BN) tm_cols *= 2;
-        rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, (uint32_t)per);
-        if (rc) return rc;
-        rc = tc_make_map(&mx, a.x, dt, (uint64_t)a.n_tok, (uint64_t)a.in, (uint64_t)a.stride_x, (uint32_t)N);
-        if (rc) return rc;
-        const uint32_t idesc_n = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        dim3 grid(n_tiles < sms ? n_tiles : sms);
-        LCU_CHECK_CUDA(launch_kernel(gemm_tcn_kernel<T>, grid, dim3(TC_THREADS), smem_n, s, pdl, a, mw, mx, n_tiles, N, BN, stages,
-                                     tm_cols, idesc_n, status));
-        g_linear_last_ctas = (int)grid.x;
-        return LCU_OK;
-    }
     // ---- weight rows on M (any output shape; row blocks of 128)
     rc = tc_make_map(&mw, a.w, dt, (uint64_t)a.out, (uint64_t)a.in, (uint64_t)a.in, 64);
     if (rc) return rc;
@@ -1003,7 +769,7 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         // 1: where it measured faster than the stream-K split (64-token blocks: 6.23 -> 6.00 ms per 8B batch-64 step;
         // very few row blocks: 11.2 -> 8.7 ms for one rank's share of the 70B shape; with 16..32 tokens and 32..48 row
         // blocks the balanced stream-K split wins: 4.75 against 4.95 ms), 2: wherever it applies, 0: never
-        static const int cluster_mode = getenv("LCU_TC_CLUSTER") ? atoi(getenv("LCU_TC_CLUSTER")) : 1;
+        const int cluster_mode = tuning().tc_cluster;
         const int n_rb_c = (n_pairs + 63) / 64, nkb_c = a.in / TC_BK;
         int KS = sms / n_rb_c;
         if (KS > 8) KS = 8;

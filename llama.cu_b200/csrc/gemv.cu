@@ -286,11 +286,6 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
 
 thread_local int g_linear_last_ctas = 0;
 
-static int tune_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-
 struct GemvPlan {
     int KS, RS, KI, RP, nwarps;
 };
@@ -322,7 +317,7 @@ static GemvPlan plan_for(int in, bool q8, int nt) {
     int cap = 8 / nt;  // keep 2*RP*NT accumulators <= 16
     if (cap < 1) cap = 1;
     if (rp > cap) rp = cap;
-    { static const int q8_rp = tune_int("LCU_Q8_RP", 4); if (q8 && rp > q8_rp) rp = q8_rp; }
+    if (q8 && rp > tuning().q8_rows) rp = tuning().q8_rows;
     best.RP = rp;
     return best;
 }
@@ -356,7 +351,7 @@ static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaS
                 set_error("gemv: configuration does not fit on an SM (in = %d, smem = %zu)", a.in, smem);
                 return LCU_ERR_INVALID;
             }
-            int cap = tune_int("LCU_GEMV_CTAS_PER_SM", 2);
+            int cap = tuning().gemv_ctas_per_sm;
             info.ctas_per_sm = occ > cap ? cap : occ;
             cache[key] = info;
         } else {

@@ -99,36 +99,6 @@ def test_reduced_shapes(L, O, name, layers, vocab, lengths, steps):
     check_parity(L, O, cfg, lengths, steps)
 
 
-@pytest.mark.parametrize("name,layers,vocab,lengths", [("tiny", 2, 2048, [16]), ("tiny", 2, 2048, [5, 40, 70]),
-                                                      ("llama8b", 2, 4096, [33]), ("llama1b", 2, 4096, [20, 90]),
-                                                      ("llama8b", 1, 2048, [600, 30, 1, 64])])
-def test_persistent_kernel_against_oracle_and_kernel_per_op(L, O, name, layers, vocab, lengths):
-    """Decode rounds of up to 4 sequences run as one persistent kernel; the kernel-per-operator
-    path is the alternative.  Both must agree with the oracle (and so with each other)."""
-    from llama_cu_b200.model import reduced
-    cfg = reduced(L.CONFIGS[name], layers, vocab)
-    prompts = prompts_for(cfg, lengths)
-    steps = 12
-    w = L.synth_weights_numpy(cfg, 0)
-    o_ids, o_lgs = O.Model(cfg, w).generate(prompts, steps)
-    ctx = L.load_model(cfg, w, kv_bytes=None)
-    results = {}
-    for mk in (True, False):
-        ctx.set_megakernel(mk)
-        g_ids = L.generate(ctx, prompts, steps)
-        launches = ctx.last_launch_count
-        g_lgs = teacher_forced_logits(L, ctx, cfg, prompts, o_ids, steps)
-        excess = max(logit_excess(g_lgs[i][s], o_lgs[i][s], cfg.act_dtype) for i in range(len(prompts)) for s in range(steps))
-        assert excess <= 0, f"megakernel={mk}: logits beyond tolerance by {excess}"
-        for i in range(len(prompts)):
-            k, margin = greedy_parity(g_ids[i], o_ids[i], o_lgs[i], TOL)
-            assert k == steps or margin <= (TOL_BF16 if cfg.act_dtype == 1 else TOL), (mk, i, k, margin)
-        assert ctx.device_status() == 0
-        results[mk] = launches
-    assert results[True] == 1 and results[False] > 5
-    ctx.close()
-
-
 def test_graph_equals_eager(L):
     """The captured decode graph and the eager launch sequence give identical ids."""
     cfg = L.CONFIGS["tiny"]

@@ -23,7 +23,7 @@ LENGTHS = (5, 9, 40)
 def spec_with(spec_path, tmp_path, **kw):
     spec = json.load(open(spec_path))
     spec.update(kw)
-    path = tmp_path / ("spec_" + "_".join(f"{k}{v}" for k, v in kw.items()) + ".json")
+    path = tmp_path / ("spec_" + "_".join(sorted(kw)) + f"_{abs(hash(json.dumps(kw, sort_keys=True))) % 10**6}.json")
     json.dump(spec, open(path, "w"))
     return path
 
@@ -94,16 +94,17 @@ def test_tp_matches_tp1_and_oracle(L, O, name, layers, vocab, tmp_path):
             got = run_world(2, spec, tmp_path, "nccl")
             assert not got["p2p"] and got["launches"] > one["launches"]  # the all-reduces are part of the step
             compare(f"{name} tp2 nccl", got, o_ids, o_lgs, one, tol, log)
-        got = run_world(world, spec, tmp_path, "p2p", {"LCU_P2P_SCATTER_RANKS": "99"})
+        got = run_world(world, spec, tmp_path, "p2p")
         assert got["p2p"]
         compare(f"{name} tp{world} p2p push", got, o_ids, o_lgs, one, tol, log)
         # the scatter (reduce-scatter + all-gather) form, forced for every round size
-        got = run_world(world, spec, tmp_path, "p2p", {"LCU_P2P_SCATTER_RANKS": "2", "LCU_P2P_SCATTER_MIN": "0"}, "_sc")
+        got = run_world(world, spec_with(spec, tmp_path, tuning={"p2p_scatter_ranks": 2, "p2p_scatter_min": 0}), tmp_path, "p2p",
+                        tag="_sc")
         assert got["p2p"]
         compare(f"{name} tp{world} p2p scatter", got, o_ids, o_lgs, one, tol, log)
         # LM head sharded by vocabulary rows: the lead rank picks among the ranks' candidates (ids cover the whole
         # vocabulary, the logits compared are the lead rank's columns)
-        got = run_world(world, spec_with(spec, tmp_path, head_shard=1), tmp_path, "p2p", {"LCU_P2P_SCATTER_RANKS": "99"}, "_hs")
+        got = run_world(world, spec_with(spec, tmp_path, head_shard=1), tmp_path, "p2p", tag="_hs")
         assert got["p2p"] and int(got["v_cols"]) == cfg.vocab // world
         compare(f"{name} tp{world} p2p push, sharded head", got, o_ids, o_lgs, one, tol, log)
 

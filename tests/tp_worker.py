@@ -50,6 +50,8 @@ def main():
     lib = L.load_library()
     comm = make_comm(lib, rank, world, dev)
 
+    for key, value in spec.get("tuning", {}).items():  # e.g. force the scatter form of the peer all-reduce
+        L.set_tuning(key, value)
     cfg = reduced(L.CONFIGS[spec["name"]], spec["layers"], spec["vocab"])
     steps = spec["steps"]
     w = L.synth_weights_numpy(cfg, 0)
