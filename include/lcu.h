@@ -229,6 +229,33 @@ LCU_API int lcu_engine_round_positions(const lcu_engine *e, uint32_t *pos_out, u
 /* One iteration of `Worker::lead`'s loop: prepare + lcu_step.  info->n_tok == 0: nothing to run. */
 LCU_API int lcu_engine_step(lcu_engine *e, lcu_stream_t stream, const float *randoms, lcu_kv_pair *out_dev,
                             lcu_round_info *info);
+/* Token budget and chunked prefill — what the reference leaves as a TODO (exec/engine_manager.rs:83,100-109: a round
+ * takes whole prompts and exec/engine.rs:68 caps it at 1024 tokens).  max_round_tokens > 0: a round holds at most that
+ * many tokens — every decoding session always gets its one, prompts share the rest in session order;
+ * prefill_chunk > 0: no prompt contributes more than that per round.  A prompt that does not finish in a round
+ * contributes a chunk whose entry in lcu_engine_round_output is LCU_ENGINE_NO_OUTPUT (ignore its pair) and which
+ * costs no step of max_steps.  0 / 0 (default): whole prompts, as the reference. */
+#define LCU_ENGINE_NO_OUTPUT (~0ull)
+LCU_API int lcu_engine_set_budget(lcu_engine *e, uint32_t max_round_tokens, uint32_t prefill_chunk);
+/* Prefix reuse == `CacheManager` (xtask/src/service/cache_manager.rs:22-66).
+ * insert: a finished session's token history and KV sequence are parked (the session id dies).
+ * send:   a new session for `tokens` starts from the parked cache sharing the longest prefix with tokens[0 .. n-1)
+ *         (the latest parked among equals; with no common prefix a parked cache is still taken and restarted at 0, as
+ *         the reference does), rolled back to that length — its pages past it return to the pool like
+ *         `KVCache::update` (exec/kv_cache.rs:34-50); without parked caches a fresh sequence.  Only tokens[pos ..] run. */
+LCU_API int lcu_engine_cache_insert(lcu_engine *e, uint64_t id, const uint32_t *tokens, uint32_t n);
+LCU_API int lcu_engine_cache_send(lcu_engine *e, const uint32_t *tokens, uint32_t n, const lcu_sample_args *args,
+                                  int max_steps, uint64_t *id_out, uint32_t *reused_out);
+LCU_API int lcu_engine_cache_count(const lcu_engine *e);
+/* Seeded sampling: with a seed lcu_engine_step draws the per-request random numbers itself (its `randoms` argument is
+ * ignored); the k-th number of a session depends only on (seed, session id, k), so a sampled conversation replays
+ * identically whatever it is batched with.  The reference draws rand::random() per row and step
+ * (exec/output_head.rs:111) and cannot be replayed.  lcu_engine_round_randoms: the numbers of the last round. */
+LCU_API int lcu_engine_set_seed(lcu_engine *e, uint64_t seed);
+/* What lcu_engine_step does under a seed, for hosts that call lcu_step themselves: draws the prepared round's numbers
+ * (one per request, 0 for arg-max rows and unfinished prefill chunks); call once per prepared round. */
+LCU_API int lcu_engine_draw_randoms(lcu_engine *e);
+LCU_API const float *lcu_engine_round_randoms(const lcu_engine *e);
 
 /* ------------------------------------------------------------------ operators
  * One entry point per `Operator::launch` implementation so a host can swap them in one

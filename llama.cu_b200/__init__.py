@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(_HERE, "liblcu.so")
 F16, BF16, F32, Q8_0, U32 = 0, 1, 2, 3, 4
 W_EMBD, W_ATTN_NORM, W_QKV, W_O, W_FFN_NORM, W_GATE_UP, W_DOWN, W_OUT_NORM, W_LM_HEAD = range(9)
 LINEAR_KINDS = (W_QKV, W_O, W_GATE_UP, W_DOWN)
+NO_OUTPUT = 2**64 - 1  # LCU_ENGINE_NO_OUTPUT: a prefill chunk that samples nothing
 OK, ERR_INVALID, ERR_CUDA, ERR_OVERFLOW, ERR_NO_PAGES, ERR_STATE, ERR_COMM, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
 
 
@@ -123,6 +124,14 @@ _SIGNATURES = {
     "lcu_engine_round_overflow": (C.POINTER(C.c_uint64), [C.c_void_p]),
     "lcu_engine_round_positions": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "lcu_engine_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(RoundInfo)]),
+    "lcu_engine_set_budget": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32]),
+    "lcu_engine_cache_insert": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32]),
+    "lcu_engine_cache_send": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(SampleArgs), C.c_int,
+                                        C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)]),
+    "lcu_engine_cache_count": (C.c_int, [C.c_void_p]),
+    "lcu_engine_set_seed": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "lcu_engine_draw_randoms": (C.c_int, [C.c_void_p]),
+    "lcu_engine_round_randoms": (C.POINTER(C.c_float), [C.c_void_p]),
     "lcu_op_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "lcu_op_fast_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_op_rms_norm": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_int,
@@ -391,4 +400,4 @@ def _view(address, n_elems, dt, device):
 
 from .model import (CONFIGS, ModelConfig, iter_synth_weights_torch, load_model, synth_weights_numpy,  # noqa: E402,F401
                     synth_weights_torch, tp_slice_numpy)
-from .host import Service, Session, StepRendezvous, generate  # noqa: E402,F401
+from .host import Service, Session, StepRendezvous, generate, generate_continuous  # noqa: E402,F401

@@ -24,7 +24,25 @@ struct Stub {  // == SessionStub + State (exec/engine.rs:33-66)
     bool active = false;
     bool has_prompt = false;
     std::vector<uint32_t> prompt;
+    uint64_t draws = 0;        // random numbers drawn for this session so far (seeded sampling)
 };
+
+// a finished conversation parked for prefix reuse == an entry of CacheManager::caches
+// (xtask/src/service/cache_manager.rs:9-12): its token history and the KV sequence that holds it
+struct Parked {
+    std::vector<uint32_t> history;
+    int seq;
+};
+
+// counter-based generator: the k-th random number of session `id` under `seed` depends on nothing else, so a
+// sampled conversation is reproducible whatever it is batched with (the reference draws rand::random() per row)
+inline float seeded_uniform(uint64_t seed, uint64_t id, uint64_t k) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull * (id + 1) + 0xBF58476D1CE4E5B9ull * (k + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (float)(z >> 40) * (1.0f / 16777216.0f);  // 24 bits -> [0, 1)
+}
 
 }  // namespace
 
@@ -39,6 +57,16 @@ struct lcu_engine {
     std::vector<lcu_req> reqs;
     std::vector<lcu_sample_args> sample;
     std::vector<uint64_t> output, finished, overflow;
+    // token budget of a round and largest prefill chunk (0: the reference's behaviour — whole prompts, no budget)
+    uint32_t max_round_tokens = 0, prefill_chunk = 0;
+    // prefix reuse
+    std::map<uint64_t, Parked> parked;  // insertion order == the reference's BTreeMap<Instant, _>
+    uint64_t park_clock = 0;
+    int next_fake_seq = 0;              // sequence labels when there is no context (host-only use)
+    // seeded sampling
+    bool seeded = false;
+    uint64_t seed = 0;
+    std::vector<float> randoms;
 };
 
 #define ENGINE_REQUIRE(cond, ...)        \
@@ -123,6 +151,19 @@ int lcu_engine_session_set_pos(lcu_engine *e, uint64_t id, uint32_t pos) {
     return LCU_OK;
 }
 
+// Token budget and chunked prefill — what the reference leaves as a TODO (exec/engine_manager.rs:83,100-109: a round
+// takes whole prompts and the engine asserts at most 1024 tokens, exec/engine.rs:68).  max_round_tokens > 0: a round
+// holds at most that many tokens; every decoding session always gets its one token, prompts share what is left in
+// session order.  prefill_chunk > 0: no prompt contributes more than that per round.  A prompt that is not finished
+// in a round contributes a chunk whose entry in the round's `output` list is LCU_ENGINE_NO_OUTPUT (its sampled pair
+// is to be ignored) and costs no step of max_steps.  0 / 0 (default): whole prompts, as the reference.
+int lcu_engine_set_budget(lcu_engine *e, uint32_t max_round_tokens, uint32_t prefill_chunk) {
+    ENGINE_REQUIRE(e, "engine_set_budget: null engine");
+    e->max_round_tokens = max_round_tokens;
+    e->prefill_chunk = prefill_chunk;
+    return LCU_OK;
+}
+
 // == `EngineManager::prepare` (exec/engine_manager.rs:72-130)
 int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info) {
     ENGINE_REQUIRE(e && info, "engine_prepare: null argument");
@@ -130,11 +171,25 @@ int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info) {
     e->output.clear(); e->finished.clear(); e->overflow.clear();
     std::map<uint64_t, size_t> pre_output;
     pre_output.swap(e->pre_output);
+    // tokens left for prompts once every decoding session has its one
+    uint64_t budget = ~0ull;
+    if (e->max_round_tokens) {
+        uint64_t n_decode = 0;
+        for (auto &kv : e->all)
+            if (kv.second.active && !kv.second.has_prompt) ++n_decode;
+        budget = e->max_round_tokens > n_decode ? e->max_round_tokens - n_decode : 0;
+    }
     size_t out_idx = 0;
     for (auto &kv : e->all) {  // std::map iterates in id order, like the reference's BTreeMap
         const uint64_t id = kv.first;
         Stub &s = kv.second;
         if (!s.active) continue;
+        uint32_t take = s.seq_len;  // tokens of this session in this round
+        if (s.has_prompt) {
+            if (e->prefill_chunk && take > e->prefill_chunk) take = e->prefill_chunk;
+            if ((uint64_t)take > budget) take = (uint32_t)budget;
+            if (take == 0) continue;  // no room in this round: the prompt waits
+        }
         const uint64_t end = (uint64_t)s.pos + s.seq_len;
         if (end > e->nctx) {  // cache overflow: the session is handed back, nothing is run for it
             e->overflow.push_back(id);
@@ -142,16 +197,23 @@ int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info) {
             continue;
         }
         const uint32_t pos = s.pos;
-        s.pos = (uint32_t)end;
+        s.pos += take;
         e->sample.push_back(s.args);
-        e->output.push_back(id);
         lcu_req rq;
         rq.seq = s.seq;
         rq.pos = pos;
-        rq.len = s.seq_len;
+        rq.len = take;
         e->reqs.push_back(rq);
-        if (s.has_prompt) {  // prefill: the whole prompt
-            e->tokens.insert(e->tokens.end(), s.prompt.begin(), s.prompt.end());
+        if (s.has_prompt) {  // prefill: the whole prompt, or its next chunk
+            budget -= take;
+            e->tokens.insert(e->tokens.end(), s.prompt.begin(), s.prompt.begin() + take);
+            if (take < s.seq_len) {  // more of the prompt to come: nothing is sampled, no step is used
+                s.prompt.erase(s.prompt.begin(), s.prompt.begin() + take);
+                s.seq_len -= take;
+                e->output.push_back(LCU_ENGINE_NO_OUTPUT);
+                ++out_idx;
+                continue;
+            }
             s.prompt.clear();
             s.has_prompt = false;
             s.seq_len = 1;
@@ -160,6 +222,7 @@ int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info) {
             e->fast_map.push_back((uint32_t)e->tokens.size());
             e->tokens.push_back(0);
         }
+        e->output.push_back(id);
         if (--s.remain_steps == 0) {
             e->finished.push_back(id);
             s.active = false;
@@ -175,6 +238,94 @@ int lcu_engine_prepare(lcu_engine *e, lcu_round_info *info) {
     info->n_overflow = (int)e->overflow.size();
     return LCU_OK;
 }
+
+// ------------------------------------------------------------------ prefix reuse == CacheManager
+// (xtask/src/service/cache_manager.rs:22-66)
+
+// == `CacheManager::insert`: a finished session's token history and KV sequence are parked for reuse.
+int lcu_engine_cache_insert(lcu_engine *e, uint64_t id, const uint32_t *tokens, uint32_t n) {
+    ENGINE_REQUIRE(e && (tokens || n == 0), "engine_cache_insert: null argument");
+    auto it = e->all.find(id);
+    ENGINE_REQUIRE(it != e->all.end(), "engine_cache_insert: unknown session");
+    ENGINE_REQUIRE(!it->second.active, "engine_cache_insert: session is running");
+    Parked p;
+    p.history.assign(tokens, tokens + n);
+    p.seq = it->second.seq;
+    e->parked[e->park_clock++] = p;
+    e->pre_output.erase(id);
+    e->all.erase(it);
+    return LCU_OK;
+}
+
+// == `CacheManager::send`: a new session for `tokens` starts from the parked cache that shares the longest prefix with
+// tokens[0 .. n-1) (the latest parked one among equals — Iterator::max_by_key keeps the last maximum; with NO common
+// prefix a parked cache is still taken and restarted at 0, as the reference does), rolled back to that length; without
+// parked caches a fresh sequence.  Only tokens[pos ..] are run.  reused_out: the number of tokens not recomputed.
+int lcu_engine_cache_send(lcu_engine *e, const uint32_t *tokens, uint32_t n, const lcu_sample_args *args, int max_steps,
+                          uint64_t *id_out, uint32_t *reused_out) {
+    ENGINE_REQUIRE(e && tokens && n > 0 && max_steps > 0 && id_out, "engine_cache_send: bad arguments");
+    bool found = false;
+    uint64_t best_key = 0;
+    uint32_t best_len = 0;
+    for (auto &kv : e->parked) {
+        const std::vector<uint32_t> &h = kv.second.history;
+        uint32_t len = 0;
+        while (len < h.size() && len + 1 < n && h[len] == tokens[len]) ++len;
+        if (!found || len >= best_len) { found = true; best_key = kv.first; best_len = len; }
+    }
+    int seq;
+    uint32_t pos = 0;
+    if (found) {
+        seq = e->parked[best_key].seq;
+        pos = best_len;
+        e->parked.erase(best_key);
+        if (e->ctx) {  // pages past the kept prefix go back to the pool, as KVCache::update does on a rollback
+            int rc = lcu_seq_resize(e->ctx, seq, pos);
+            if (rc) return rc;
+        }
+    } else if (e->ctx) {
+        int rc = lcu_seq_create(e->ctx, &seq);
+        if (rc) return rc;
+    } else {
+        seq = e->next_fake_seq++;
+    }
+    int rc = lcu_engine_session_new(e, seq, args, id_out);
+    if (rc) return rc;
+    e->all[*id_out].pos = pos;
+    if (reused_out) *reused_out = pos;
+    return lcu_engine_start(e, *id_out, tokens + pos, n - pos, max_steps);
+}
+
+int lcu_engine_cache_count(const lcu_engine *e) { return e ? (int)e->parked.size() : 0; }
+
+// ------------------------------------------------------------------ seeded sampling
+// With a seed the engine draws the per-request random numbers itself: the k-th number of a session depends only on
+// (seed, session id, k).  The reference's host draws rand::random() per row and step (exec/output_head.rs:111) and
+// cannot be replayed.
+int lcu_engine_set_seed(lcu_engine *e, uint64_t seed) {
+    ENGINE_REQUIRE(e, "engine_set_seed: null engine");
+    e->seeded = true;
+    e->seed = seed;
+    return LCU_OK;
+}
+
+// Draws the random numbers of the prepared round (one per request; 0 for arg-max rows and unfinished prefill
+// chunks) and advances the sessions' draw counters: what lcu_engine_step does under a seed, for hosts that call
+// lcu_step themselves.  Call once per prepared round.
+int lcu_engine_draw_randoms(lcu_engine *e) {
+    ENGINE_REQUIRE(e && e->seeded, "engine_draw_randoms: no seed set");
+    e->randoms.assign(e->reqs.size(), 0.f);
+    for (size_t i = 0; i < e->reqs.size(); ++i) {
+        const lcu_sample_args &a = e->sample[i];
+        if (e->output[i] == LCU_ENGINE_NO_OUTPUT || a.temperature == 0.f || a.top_k == 1) continue;
+        Stub &st = e->all[e->output[i]];
+        e->randoms[i] = seeded_uniform(e->seed, e->output[i], st.draws++);
+    }
+    return LCU_OK;
+}
+
+// the numbers of the last lcu_engine_draw_randoms / seeded lcu_engine_step
+const float *lcu_engine_round_randoms(const lcu_engine *e) { return e && e->seeded ? e->randoms.data() : nullptr; }
 
 const uint32_t *lcu_engine_round_tokens(const lcu_engine *e) { return e ? e->tokens.data() : nullptr; }
 const lcu_req *lcu_engine_round_reqs(const lcu_engine *e) { return e ? e->reqs.data() : nullptr; }
@@ -208,6 +359,11 @@ int lcu_engine_step(lcu_engine *e, lcu_stream_t stream, const float *randoms, lc
     bool any_sampling = false;
     for (const lcu_sample_args &a : e->sample)
         if (!(a.temperature == 0.f || a.top_k == 1)) any_sampling = true;
+    if (e->seeded) {
+        rc = lcu_engine_draw_randoms(e);
+        if (rc) return rc;
+        randoms = e->randoms.data();
+    }
     return lcu_step(e->ctx, stream, info->n_req, e->reqs.data(), e->tokens.data(), any_sampling ? e->sample.data() : nullptr,
                     any_sampling ? randoms : nullptr, e->fast_map.empty() ? nullptr : e->fast_map.data(), info->n_fast,
                     out_dev);

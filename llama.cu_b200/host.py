@@ -9,7 +9,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from . import RoundInfo, SampleArgs, check, load_library, stream_ptr
+from . import NO_OUTPUT, RoundInfo, SampleArgs, check, load_library, stream_ptr
 
 
 @dataclass
@@ -92,6 +92,42 @@ class Service:
         p = np.ascontiguousarray(prompt, dtype=np.uint32)
         check(self.lib.lcu_engine_start(self.e, session.id, p.ctypes.data, len(p), max_steps))
 
+    def set_budget(self, max_round_tokens=0, prefill_chunk=0):
+        """Token budget of a round and largest prefill chunk (chunked prefill; 0 / 0 = whole prompts as the reference)."""
+        check(self.lib.lcu_engine_set_budget(self.e, max_round_tokens, prefill_chunk))
+
+    def set_seed(self, seed):
+        """Reproducible sampling: the engine draws the random numbers itself from (seed, session, draw index)."""
+        check(self.lib.lcu_engine_set_seed(self.e, seed))
+
+    def draw_randoms(self, n_req):
+        """The seeded random numbers of the round just prepared (advances the sessions' draw counters)."""
+        check(self.lib.lcu_engine_draw_randoms(self.e))
+        p = self.lib.lcu_engine_round_randoms(self.e)
+        return [p[i] for i in range(n_req)]
+
+    def park(self, session, tokens):
+        """== `CacheManager::insert`: park a finished session's history and cache for prefix reuse."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        check(self.lib.lcu_engine_cache_insert(self.e, session.id, t.ctypes.data, len(t)))
+        self.sessions.pop(session.id, None)
+
+    def send(self, tokens, sample_args=None, max_steps=1):
+        """== `CacheManager::send`: start `tokens` on the parked cache with the longest common prefix (or a fresh one).
+        Returns (session, tokens reused from the cache)."""
+        t = np.ascontiguousarray(tokens, dtype=np.uint32)
+        args = sample_args or SampleArgs.arg_max()
+        sid, reused = C.c_uint64(), C.c_uint32()
+        check(self.lib.lcu_engine_cache_send(self.e, t.ctypes.data, len(t), C.byref(args), max_steps, C.byref(sid),
+                                             C.byref(reused)))
+        s = Session(sid.value, -1, args, self)
+        self.sessions[s.id] = s
+        return s, reused.value
+
+    @property
+    def parked(self):
+        return self.lib.lcu_engine_cache_count(self.e)
+
     def stop(self, session_id):
         check(self.lib.lcu_engine_remove(self.e, session_id))
         return self.sessions.get(session_id)
@@ -109,6 +145,7 @@ class Service:
         output = [(out_p[i], 1) for i in range(info.n_req)]
         fin_p = lib.lcu_engine_round_finished(e)
         finished = [self.sessions[fin_p[i]] for i in range(info.n_finished)]
+        output = [(sid, n) if sid != NO_OUTPUT else (None, 0) for sid, n in output]  # unfinished prefill chunks sample nothing
         ov_p = lib.lcu_engine_round_overflow(e)
         overflow = [self.sessions[ov_p[i]] for i in range(info.n_overflow)]
         return Round(overflow, tokens, reqs, sample, output, fast_map, finished)
@@ -147,7 +184,7 @@ class Service:
     def decode(round_, out):
         """== `exec::decode` (exec/mod.rs:91-115): D2H of the pairs, split per session."""
         host = out[:len(round_.output)].cpu().numpy().view(np.uint32)
-        return {sid: int(host[i, 0]) for i, (sid, _) in enumerate(round_.output)}
+        return {sid: int(host[i, 0]) for i, (sid, _) in enumerate(round_.output) if sid is not None}
 
 
 def generate(ctx, prompts, steps, sample_args=None, read_every_step=False, randoms=None):
@@ -229,3 +266,33 @@ class StepRendezvous:
             if time.monotonic() > limit:
                 raise LcuError(ERR_TIMEOUT, f"round {step}: rank(s) {gone} never arrived")
             time.sleep(0.002)
+
+
+def generate_continuous(ctx, prompts, steps, max_round_tokens=0, prefill_chunk=0, sample_args=None, seed=None):
+    """All prompts enter the batch together and run under a token budget with chunked prefill (`Service.set_budget`):
+    long prompts are fed a chunk per round while sessions that have finished theirs already decode.  Returns
+    [n_prompts][steps] token ids.  (The reference admits whole prompts only, at most 1024 tokens per round.)"""
+    import torch
+    svc = Service(ctx)
+    svc.set_budget(max_round_tokens, prefill_chunk)
+    if seed is not None:
+        svc.set_seed(seed)
+    with torch.cuda.stream(svc.stream):
+        sessions = [svc.new_session(sample_args) for _ in prompts]
+        for s, p in zip(sessions, prompts):
+            svc.start(s, p, steps)
+        toks = {s.id: [] for s in sessions}
+        pending = []
+        while True:
+            r, out = svc.step()
+            if out is None:
+                break
+            pending.append((r, out.clone()))
+        svc.stream.synchronize()
+        torch.cuda.synchronize(ctx.device)
+        for r, out in pending:
+            for sid, t in Service.decode(r, out).items():
+                toks[sid].append(t)
+    for s in sessions:
+        ctx.seq_free(s.seq)
+    return [toks[s.id] for s in sessions]

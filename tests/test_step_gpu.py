@@ -130,3 +130,28 @@ def test_overflow_and_pages(L):
     assert ctx.pages_free == ctx2_pages
     torch.cuda.synchronize()
     ctx.close()
+
+
+@pytest.mark.parametrize("name,layers,vocab,lengths,budget,chunk", [
+    ("tiny", 2, 2048, [1000, 3, 70], 256, 200),      # a 1000-token prompt in chunks of 200 while two others decode
+    ("llama8b", 2, 4096, [300, 20], 128, 0),         # budget only: 127- and 128-token slices of the long prompt
+])
+def test_chunked_prefill_equals_whole_prompt_prefill(L, O, name, layers, vocab, lengths, budget, chunk):
+    """A prompt fed in chunks under a token budget gives the tokens of the unchunked run: greedy ids identical to the
+    staged whole-prompt prefill and to the oracle, except past a step where the oracle's top-2 margin is a tie."""
+    from llama_cu_b200.model import reduced
+    cfg = reduced(L.CONFIGS[name], layers, vocab)
+    steps = 12
+    prompts = prompts_for(cfg, lengths)
+    w = L.synth_weights_numpy(cfg, 0)
+    o_ids, o_lgs = O.Model(cfg, w).generate(prompts, steps)
+    ctx = L.load_model(cfg, w, kv_bytes=None, max_seqs=len(prompts))
+    whole = L.generate(ctx, prompts, steps)
+    chunked = L.generate_continuous(ctx, prompts, steps, max_round_tokens=budget, prefill_chunk=chunk)
+    assert ctx.device_status() == 0
+    for i in range(len(prompts)):
+        for got in (whole[i], chunked[i]):
+            assert len(got) == steps
+            k, margin = greedy_parity(got, o_ids[i], o_lgs[i], TOL)
+            assert k == steps or margin <= TOL, (i, k, margin)
+    ctx.close()
