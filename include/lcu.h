@@ -257,6 +257,30 @@ LCU_API int lcu_engine_set_seed(lcu_engine *e, uint64_t seed);
 LCU_API int lcu_engine_draw_randoms(lcu_engine *e);
 LCU_API const float *lcu_engine_round_randoms(const lcu_engine *e);
 
+/* ------------------------------------------------------------------ GGUF model files
+ * == `GGufModel::read` / `merge` (model/gguf.rs:16-72), the metadata -> shape mapping of `GGufModel::llama`
+ * (model/mod.rs:61-182) and the weight upload of `load_weight` (load/mod.rs:23-108).  Files use the reference's tensor
+ * naming: fused `blk.N.attn_qkv.weight` (rows q|k|v) and `blk.N.ffn_gate_up.weight` (rows gate|up); `output.weight`
+ * falls back to `token_embd.weight`.  F16 / BF16 models, F16 / BF16 / F32 norm weights, and Q8_0 linear weights
+ * (repacked at load time — the reference itself cannot run them).  Shards: every path is one file of a split model;
+ * `general.alignment` and `split.*` keys are per file, any other key may repeat only with the same value. */
+typedef struct lcu_gguf lcu_gguf;
+LCU_API int lcu_gguf_open(const char *const *paths, int n_paths, lcu_gguf **out);
+LCU_API int lcu_gguf_close(lcu_gguf *g); /* also frees the device region lcu_gguf_load filled */
+LCU_API int lcu_gguf_n_tensors(const lcu_gguf *g);
+/* name (valid until close), lcu_dtype, dims outermost first (the reference reverses ggml's order too, gguf.rs:56-61) */
+LCU_API int lcu_gguf_tensor_info(const lcu_gguf *g, int index, const char **name, int *dtype, uint64_t dims4[4], int *n_dims,
+                                 size_t *bytes);
+LCU_API int lcu_gguf_meta_u64(const lcu_gguf *g, const char *key, uint64_t *out);
+LCU_API int lcu_gguf_meta_f32(const lcu_gguf *g, const char *key, float *out);
+LCU_API int lcu_gguf_meta_str(const lcu_gguf *g, const char *key, char *buf, size_t cap, size_t *len);
+/* Fills the model fields of *desc; nctx, page_tokens, max_tokens, max_seqs are the caller's when non-zero on entry. */
+LCU_API int lcu_gguf_model_desc(const lcu_gguf *g, lcu_model_desc *desc);
+/* Uploads every weight of `ctx`'s rank into ONE device region owned by the handle (keep it open while the context is
+ * in use) through two pinned slabs, cuts linear weights per rank, repacks Q8_0, registers each with lcu_set_weight.
+ * Synchronises `stream` as it goes; call with `ctx`'s device current. */
+LCU_API int lcu_gguf_load(lcu_gguf *g, lcu_ctx *ctx, lcu_stream_t stream);
+
 /* ------------------------------------------------------------------ operators
  * One entry point per `Operator::launch` implementation so a host can swap them in one
  * at a time behind `launch_nn_exec` (exec/step.rs:101-138).  dt = activation dtype. */

@@ -132,6 +132,16 @@ _SIGNATURES = {
     "lcu_engine_set_seed": (C.c_int, [C.c_void_p, C.c_uint64]),
     "lcu_engine_draw_randoms": (C.c_int, [C.c_void_p]),
     "lcu_engine_round_randoms": (C.POINTER(C.c_float), [C.c_void_p]),
+    "lcu_gguf_open": (C.c_int, [C.POINTER(C.c_char_p), C.c_int, C.POINTER(C.c_void_p)]),
+    "lcu_gguf_close": (C.c_int, [C.c_void_p]),
+    "lcu_gguf_n_tensors": (C.c_int, [C.c_void_p]),
+    "lcu_gguf_tensor_info": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_uint64),
+                                       C.POINTER(C.c_int), C.POINTER(C.c_size_t)]),
+    "lcu_gguf_meta_u64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "lcu_gguf_meta_f32": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_float)]),
+    "lcu_gguf_meta_str": (C.c_int, [C.c_void_p, C.c_char_p, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "lcu_gguf_model_desc": (C.c_int, [C.c_void_p, C.POINTER(ModelDesc)]),
+    "lcu_gguf_load": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "lcu_op_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "lcu_op_fast_embedding": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "lcu_op_rms_norm": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_int,
@@ -382,6 +392,69 @@ class Context:
     @property
     def last_step_bytes(self):
         return self.lib.lcu_last_step_bytes(self.h)
+
+
+class GGuf:
+    """A (possibly split) GGUF model: metadata, tensor table, upload into a Context (`lcu_gguf_*`)."""
+
+    def __init__(self, paths):
+        self.lib = load_library()
+        paths = [paths] if isinstance(paths, (str, bytes, os.PathLike)) else list(paths)
+        arr = (C.c_char_p * len(paths))(*[os.fsencode(p) for p in paths])
+        h = C.c_void_p()
+        check(self.lib.lcu_gguf_open(arr, len(paths), C.byref(h)))
+        self.h = h
+
+    def close(self):
+        if self.h:
+            self.lib.lcu_gguf_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensors(self):
+        """[(name, lcu dtype, dims outermost first, bytes)] in file order."""
+        out = []
+        for i in range(self.lib.lcu_gguf_n_tensors(self.h)):
+            name, dt, nd, nb = C.c_char_p(), C.c_int(), C.c_int(), C.c_size_t()
+            dims = (C.c_uint64 * 4)()
+            check(self.lib.lcu_gguf_tensor_info(self.h, i, C.byref(name), C.byref(dt), dims, C.byref(nd), C.byref(nb)))
+            out.append((name.value.decode(), dt.value, tuple(dims[:nd.value]), nb.value))
+        return out
+
+    def meta_u64(self, key):
+        v = C.c_uint64()
+        check(self.lib.lcu_gguf_meta_u64(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def meta_f32(self, key):
+        v = C.c_float()
+        check(self.lib.lcu_gguf_meta_f32(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def meta_str(self, key):
+        n = C.c_size_t()
+        check(self.lib.lcu_gguf_meta_str(self.h, key.encode(), None, 0, C.byref(n)))
+        buf = C.create_string_buffer(n.value + 1)
+        check(self.lib.lcu_gguf_meta_str(self.h, key.encode(), buf, n.value + 1, None))
+        return buf.value.decode()
+
+    def model_desc(self, nctx=0, page_tokens=0, max_tokens=0, max_seqs=0):
+        d = ModelDesc()
+        d.nctx, d.page_tokens, d.max_tokens, d.max_seqs = nctx, page_tokens, max_tokens, max_seqs
+        check(self.lib.lcu_gguf_model_desc(self.h, C.byref(d)))
+        return d
+
+    def load(self, ctx, stream=None):
+        """Uploads this rank's weights into `ctx` (the handle owns the device memory: keep it alive)."""
+        import torch
+        with torch.cuda.device(ctx.device):
+            check(self.lib.lcu_gguf_load(self.h, ctx.h, stream_ptr(stream)))
+        ctx._keep.append(self)
 
 
 class _RawDevice:

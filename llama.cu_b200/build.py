@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "_obj")
 LIB = os.path.join(HERE, "liblcu.so")
-SOURCES = ["ctx.cu", "api.cu", "ops.cu", "gemv.cu", "attention.cu", "sample.cu", "comm.cu", "gemm_skinny.cu", "gemm_tc.cu", "p2p.cu", "engine.cpp"]
+SOURCES = ["ctx.cu", "api.cu", "ops.cu", "gemv.cu", "attention.cu", "sample.cu", "comm.cu", "gemm_skinny.cu", "gemm_tc.cu", "p2p.cu", "engine.cpp", "gguf.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

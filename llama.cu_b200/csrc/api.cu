@@ -65,12 +65,10 @@ int lcu_tp_slice_weight(const lcu_ctx *ctx, int kind, void *dst, const void *src
     LCU_REQUIRE(ctx && dst && src, "tp_slice_weight: null argument");
     CtxShape c = ctx_shape(ctx);
     cudaStream_t s = as_stream(stream);
-    const size_t eb = 2;
     const bool linear = kind == LCU_W_QKV || kind == LCU_W_O || kind == LCU_W_GATE_UP || kind == LCU_W_DOWN;
-    LCU_REQUIRE(!(linear && c.weight_dtype == LCU_Q8_0 && c.tp_size > 1), "tp_slice_weight: slicing Q8_0 weights is not supported");
     if (kind == LCU_W_LM_HEAD && c.tp_size > 1 && c.tp_rank != 0) {
         // rows [rank * vocab / tp, (rank + 1) * vocab / tp) when the head can be sharded (lcu_weight_bytes says so)
-        const size_t bytes = lcu_weight_bytes(ctx, kind), full = (size_t)c.vocab * c.d * eb;
+        const size_t bytes = lcu_weight_bytes(ctx, kind), full = (size_t)c.vocab * c.d * 2;
         const size_t off = bytes < full ? (size_t)c.tp_rank * bytes : 0;
         LCU_CHECK_CUDA(cudaMemcpyAsync(dst, reinterpret_cast<const unsigned char *>(src) + off, bytes, cudaMemcpyDeviceToDevice, s));
         return LCU_OK;
@@ -79,33 +77,55 @@ int lcu_tp_slice_weight(const lcu_ctx *ctx, int kind, void *dst, const void *src
         LCU_CHECK_CUDA(cudaMemcpyAsync(dst, src, lcu_weight_bytes(ctx, kind), cudaMemcpyDeviceToDevice, s));
         return LCU_OK;
     }
+    // The cut `TPAction::move_data` makes with Distribution{start = rank, len = 1, total = tp} (load/mod.rs:86-99):
+    // up to three row segments of the full matrix and one column range, in elements.
     const int tp = c.tp_size, r = c.tp_rank;
     const size_t nh_l = c.nh / tp, nkvh_l = c.nkvh / tp, di_l = c.di / tp, dh = c.dh, d = c.d;
-    unsigned char *out = reinterpret_cast<unsigned char *>(dst);
-    int rc = LCU_OK;
+    struct Seg { size_t r0, nr; } seg[3];
+    int n_seg = 0;
+    size_t full_cols = 0, c0 = 0, nc = 0;
     switch (kind) {
-    case LCU_W_QKV: {  // rows q | k | v, each split by heads
-        size_t pitch = d * eb;
-        rc = copy_block(out, pitch, src, pitch, r * nh_l * dh, nh_l * dh, 0, pitch, s);
-        if (rc) return rc;
-        out += nh_l * dh * pitch;
-        rc = copy_block(out, pitch, src, pitch, (size_t)c.nh * dh + r * nkvh_l * dh, nkvh_l * dh, 0, pitch, s);
-        if (rc) return rc;
-        out += nkvh_l * dh * pitch;
-        return copy_block(out, pitch, src, pitch, (size_t)(c.nh + c.nkvh) * dh + r * nkvh_l * dh, nkvh_l * dh, 0, pitch, s);
-    }
+    case LCU_W_QKV:  // rows q | k | v, each split by heads
+        seg[0] = {r * nh_l * dh, nh_l * dh};
+        seg[1] = {(size_t)c.nh * dh + r * nkvh_l * dh, nkvh_l * dh};
+        seg[2] = {(size_t)(c.nh + c.nkvh) * dh + r * nkvh_l * dh, nkvh_l * dh};
+        n_seg = 3; full_cols = d; c0 = 0; nc = d;
+        break;
     case LCU_W_O:  // input columns split by heads
-        return copy_block(out, nh_l * dh * eb, src, (size_t)c.nh * dh * eb, 0, d, r * nh_l * dh * eb, nh_l * dh * eb, s);
-    case LCU_W_GATE_UP: {  // rows gate | up, each split
-        size_t pitch = d * eb;
-        rc = copy_block(out, pitch, src, pitch, r * di_l, di_l, 0, pitch, s);
-        if (rc) return rc;
-        return copy_block(out + di_l * pitch, pitch, src, pitch, (size_t)c.di + r * di_l, di_l, 0, pitch, s);
+        seg[0] = {0, d};
+        n_seg = 1; full_cols = (size_t)c.nh * dh; c0 = r * nh_l * dh; nc = nh_l * dh;
+        break;
+    case LCU_W_GATE_UP:  // rows gate | up, each split
+        seg[0] = {r * di_l, di_l};
+        seg[1] = {(size_t)c.di + r * di_l, di_l};
+        n_seg = 2; full_cols = d; c0 = 0; nc = d;
+        break;
+    default:  // LCU_W_DOWN: input columns split
+        seg[0] = {0, d};
+        n_seg = 1; full_cols = (size_t)c.di; c0 = r * di_l; nc = di_l;
+        break;
     }
-    case LCU_W_DOWN:  // input columns split
-        return copy_block(out, di_l * eb, src, (size_t)c.di * eb, 0, d, r * di_l * eb, di_l * eb, s);
-    }
-    return LCU_OK;
+    size_t full_rows = kind == LCU_W_QKV ? (size_t)(c.nh + 2 * c.nkvh) * dh : (kind == LCU_W_GATE_UP ? (size_t)2 * c.di : d);
+    // one plane of `eb`-byte elements whose columns are the matrix columns divided by `per`
+    auto plane = [&](unsigned char *out, const unsigned char *in, size_t eb, size_t per) -> int {
+        const size_t src_pitch = full_cols / per * eb, dst_pitch = nc / per * eb;
+        for (int i = 0; i < n_seg; ++i) {
+            int rc = copy_block(out, dst_pitch, in, src_pitch, seg[i].r0, seg[i].nr, c0 / per * eb, dst_pitch, s);
+            if (rc) return rc;
+            out += seg[i].nr * dst_pitch;
+        }
+        return LCU_OK;
+    };
+    unsigned char *out = reinterpret_cast<unsigned char *>(dst);
+    const unsigned char *in = reinterpret_cast<const unsigned char *>(src);
+    if (c.weight_dtype != LCU_Q8_0) return plane(out, in, 2, 1);
+    // Q8_0 in the plane layout (lcu_repack_q8_0): int8 [rows, cols] followed by f16 scales [rows, cols / 32]
+    LCU_REQUIRE(c0 % 32 == 0 && nc % 32 == 0, "tp_slice_weight: Q8_0 column range [%zu, +%zu) is not a multiple of 32", c0, nc);
+    size_t my_rows = 0;
+    for (int i = 0; i < n_seg; ++i) my_rows += seg[i].nr;
+    int rc = plane(out, in, 1, 1);
+    if (rc) return rc;
+    return plane(out + my_rows * nc, in + full_rows * full_cols, 2, 32);
 }
 
 // ------------------------------------------------------------------ operators

@@ -114,3 +114,65 @@ def parity_report(g_lgs, g_ids, o_lgs, o_ids, tol):
                 lg = np.sort(o_lgs[i][s])
                 off.append((i, s, float(lg[-1] - lg[-2])))
     return worst, exact, total, off
+
+
+def write_gguf(paths, cfg, weights, norm_f32=True, tied=False, extra_meta=None):
+    """Writes the model as GGUF with the reference's tensor naming (fused attn_qkv / ffn_gate_up) using the `gguf`
+    package; `paths` with several entries splits the tensors round-robin over shards (metadata in the first shard,
+    `general.architecture` — which the writer always emits — in all of them).  `weights` as from synth_weights_numpy."""
+    import gguf
+    from llama_cu_b200 import (F16, Q8_0, W_ATTN_NORM, W_DOWN, W_EMBD, W_FFN_NORM, W_GATE_UP, W_LM_HEAD, W_O, W_OUT_NORM,
+                               W_QKV)
+    paths = [paths] if isinstance(paths, str) else list(paths)
+    writers = [gguf.GGUFWriter(p, "llama") for p in paths]
+    w0 = writers[0]
+    w0.add_block_count(cfg.n_layers)
+    w0.add_context_length(cfg.nctx)
+    w0.add_embedding_length(cfg.d)
+    w0.add_head_count(cfg.nh)
+    w0.add_head_count_kv(cfg.nkvh)
+    w0.add_rope_dimension_count(cfg.dh)
+    w0.add_feed_forward_length(cfg.di)
+    w0.add_layer_norm_rms_eps(cfg.eps)
+    w0.add_rope_freq_base(cfg.theta)
+    w0.add_token_list([f"t{i}" for i in range(cfg.vocab)])
+    for k, v in (extra_meta or {}).items():
+        w0.add_uint32(k, v)
+    for i, w in enumerate(writers[1:], 1):
+        w.add_uint16("split.no", i)
+
+    def dense(bits):
+        if cfg.act_dtype == F16:
+            return bits.view(np.float16), None
+        return bits.view(np.uint8).reshape(bits.shape[0], -1), gguf.GGMLQuantizationType.BF16
+
+    def norm(bits):
+        if norm_f32:
+            f = bits.view(np.float16).astype(np.float32) if cfg.act_dtype == F16 else (bits.astype(np.uint32) << 16).view(np.float32)
+            return f, None
+        return dense(bits.reshape(1, -1))[0].reshape(-1), (None if cfg.act_dtype == F16 else gguf.GGMLQuantizationType.BF16)
+
+    def linear(w):
+        if isinstance(w, dict):
+            rows, cols = w["q"].shape
+            return w["blocks"].reshape(rows, cols // 32 * 34), gguf.GGMLQuantizationType.Q8_0
+        return dense(w)
+
+    items = [("token_embd.weight", dense(weights[(-1, W_EMBD)]))]
+    for l in range(cfg.n_layers):
+        items += [(f"blk.{l}.attn_norm.weight", norm(weights[(l, W_ATTN_NORM)])),
+                  (f"blk.{l}.attn_qkv.weight", linear(weights[(l, W_QKV)])),
+                  (f"blk.{l}.attn_output.weight", linear(weights[(l, W_O)])),
+                  (f"blk.{l}.ffn_norm.weight", norm(weights[(l, W_FFN_NORM)])),
+                  (f"blk.{l}.ffn_gate_up.weight", linear(weights[(l, W_GATE_UP)])),
+                  (f"blk.{l}.ffn_down.weight", linear(weights[(l, W_DOWN)]))]
+    items.append(("output_norm.weight", norm(weights[(-1, W_OUT_NORM)])))
+    if not tied:
+        items.append(("output.weight", dense(weights[(-1, W_LM_HEAD)])))
+    for i, (name, (arr, raw)) in enumerate(items):
+        writers[i % len(writers)].add_tensor(name, np.ascontiguousarray(arr), raw_dtype=raw)
+    for w in writers:
+        w.write_header_to_file()
+        w.write_kv_data_to_file()
+        w.write_tensors_to_file()
+        w.close()
