@@ -714,10 +714,10 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     // One linear layer over `n` rows: token groups of <= 4 through the GEMV (RMSNorm fused as its
     // prologue), or blocks of <= 64 through the tensor-core kernel (activations normalised before).
     const bool p2p = c->tp_size > 1 && c->p2p.ready;
-    // large rounds may reduce-scatter + all-gather through the column owners instead of pushing everything to everyone
-    // (tuning: p2p_scatter_ranks / p2p_scatter_min; off by default — measured on the 70B shape, 64 tokens per round:
-    // 16.9 ms per step with the push form against 17.5 ms with this one on 4 ranks; with 2 ranks both forms move the
-    // same bytes and this one only adds a hop)
+    // large rounds reduce-scatter + all-gather through the column owners instead of pushing everything to everyone:
+    // 2 (n - 1) / n of the message per rank instead of (n - 1), for one more hop.  Measured on the 70B shape with 64
+    // tokens per round (1 MiB messages): 17.5 ms per step against 16.9 ms for the push form on 4 ranks, 12.5 against
+    // 15.0 ms on 8 — so from 8 ranks on (tuning: p2p_scatter_ranks) for rounds of 128 KB and more (p2p_scatter_min).
     const long scatter_min = tuning().p2p_scatter_min;
     const int scatter_ranks = tuning().p2p_scatter_ranks;
     const int scatter_cols = (p2p && c->tp_size >= scatter_ranks && (long)r.n_tok * d.d * 2 >= scatter_min &&
