@@ -38,6 +38,7 @@ struct Tuning {
     int gemv_ctas_per_sm = 2;      // GEMV CTAs per SM (read at a shape's first launch)
     int q8_rows = 4;               // Q8_0 GEMV: row pairs per thread
     int tc = 1;                    // 0: keep the tcgen05 kernel out (mma.sync kernel for every batched round)
+    int tc_block = 256;            // most tokens one tcgen05 launch takes (64, 128, 256): prefill rounds are cut into such blocks
     int tc_cluster = 1;            // cluster split-K form of the tcgen05 kernel: 0 never, 1 where it measured faster, 2 wherever it applies
     int p2p_scatter_ranks = 8;     // ranks from which the peer all-reduce takes the reduce-scatter + all-gather form
     long p2p_scatter_min = 131072; // ... for rounds of at least this many bytes

@@ -594,6 +594,7 @@ int lcu_set_tuning(lcu_ctx *c, const char *key, long long value) {
     else if (k == "gemv_ctas_per_sm") { LCU_REQUIRE(value >= 1 && value <= 2, "set_tuning: gemv_ctas_per_sm = %lld (1, 2)", value); t.gemv_ctas_per_sm = (int)value; }
     else if (k == "q8_rows") { LCU_REQUIRE(value == 1 || value == 2 || value == 4, "set_tuning: q8_rows = %lld (1, 2, 4)", value); t.q8_rows = (int)value; }
     else if (k == "tc") t.tc = value != 0;
+    else if (k == "tc_block") { LCU_REQUIRE(value == 64 || value == 128 || value == 256, "set_tuning: tc_block = %lld (64, 128, 256)", value); t.tc_block = (int)value; }
     else if (k == "tc_cluster") { LCU_REQUIRE(value >= 0 && value <= 2, "set_tuning: tc_cluster = %lld (0..2)", value); t.tc_cluster = (int)value; }
     else if (k == "p2p_scatter_ranks") t.p2p_scatter_ranks = (int)value;
     else if (k == "p2p_scatter_min") t.p2p_scatter_min = (long)value;
@@ -741,7 +742,9 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
         }
         for (int t0 = 0; t0 < n;) {
             int nt;
-            if (batched) nt = n - t0 < 64 ? n - t0 : 64;
+            // token blocks of up to 256 on the tcgen05 path (a weight tile is then streamed once per 256 tokens), 64 otherwise
+            const int blk = (tc_on && gemm_tc_supported(proto.in, proto.w_q8)) ? tuning().tc_block : 64;
+            if (batched) nt = n - t0 < blk ? n - t0 : blk;
             else {
                 nt = gemv_max_tokens(proto.in);
                 if (nt > n - t0) nt = n - t0;

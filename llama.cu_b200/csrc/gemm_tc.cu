@@ -504,6 +504,9 @@ __device__ __forceinline__ float4 tc_ld_dsmem4(uint32_t local_saddr, uint32_t ct
     return v;
 }
 
+// Token blocks of 128 and 256 (prefill): the MMA takes all N tokens at once (tcgen05 allows N up to 256 columns of
+// TMEM per accumulator), so a weight tile is streamed once per 256 tokens instead of once per 64; the epilogue then
+// walks the accumulator in passes of NS = 64 tokens through the same staging tile and the same two cluster barriers.
 template <class T>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -511,8 +514,9 @@ gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, con
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (tc_smem(smem_raw) & 1023u)) & 1023u);
     const int stage_bytes = TC_A_BYTES + N * 128;
-    float *stg = reinterpret_cast<float *>(smem + (size_t)n_stages * stage_bytes);  // [N][TCK_LD]
-    TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)N * TCK_LD * 4);
+    const int NS = N > 64 ? 64 : N;  // tokens per epilogue pass
+    float *stg = reinterpret_cast<float *>(smem + (size_t)n_stages * stage_bytes);  // [NS][TCK_LD]
+    TcShared *sh = reinterpret_cast<TcShared *>(reinterpret_cast<unsigned char *>(stg) + (size_t)NS * TCK_LD * 4);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (a.pdl_trigger == 0) grid_dep_launch();
@@ -542,6 +546,7 @@ gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = sh->tmem_base;
 
+    bool ok = true;  // epilogue warps: the accumulator is complete
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer (weights of the first ring before the dependency wait, as in gemm_tc_kernel)
         auto issue = [&](int j, bool weights, bool acts) {
@@ -589,62 +594,68 @@ gemm_tck_kernel(const GemvArgs a, const __grid_constant__ CUtensorMap map_w, con
         }
         tc_commit(tc_smem(&sh->tmem_full[0]));
     } else if (warp >= 2) {
-        // ---------------- accumulator -> token-major staging tile
-        const int q = warp & 3;
-        const int row = q * 32 + lane;
-        bool ok = tc_mbar_wait(tc_smem(&sh->tmem_full[0]), 0u, &sh->abort_flag);
+        ok = tc_mbar_wait(tc_smem(&sh->tmem_full[0]), 0u, &sh->abort_flag);
         if (!ok) {
             atomicOr(status, 4u);
             sh->abort_flag = 1;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int c0 = 0; c0 < N; c0 += 16) {
-            uint32_t r[16];
-            if (ok) {
-                tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) stg[(size_t)(c0 + i) * TCK_LD + row] = ok ? __uint_as_float(r[i]) : 0.f;
-        }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    tc_cluster_sync();  // every CTA of the row block has staged its partial tile
 
-    if (warp >= 2) {
-        // ---------------- this CTA's share of the items: chunk c of 8 rows (8 pairs for SwiGLU) with c % KS == ks
-        const int et = tid - 64;
-        const int chunks = swiglu ? 8 : 16;
-        const int mine = (chunks - ks + KS - 1) / KS;  // chunks ks, ks + KS, ...
-        TcPre pre[8];
-        int cnt = 0;
-        for (int idx = et; idx < mine * N; idx += 128, ++cnt) {
-            const int c = ks + (idx % mine) * KS, n = idx / mine;
-            const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
-            if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
-        }
-        cnt = 0;
-        for (int idx = et; idx < mine * N; idx += 128, ++cnt) {
-            const int c = ks + (idx % mine) * KS, n = idx / mine;
-            const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
-            if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
-            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            const uint32_t sv = tc_smem(stg + (size_t)n * TCK_LD + 8 * c);
-            for (int p = 0; p < KS; ++p) {
-                const float4 lo = tc_ld_dsmem4(sv, (uint32_t)p), hi = tc_ld_dsmem4(sv + 16, (uint32_t)p);
-                v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
-                v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
-                if (swiglu) {
-                    const float4 l2 = tc_ld_dsmem4(sv + 64 * 4, (uint32_t)p), h2 = tc_ld_dsmem4(sv + 64 * 4 + 16, (uint32_t)p);
-                    u[0] += l2.x; u[1] += l2.y; u[2] += l2.z; u[3] += l2.w;
-                    u[4] += h2.x; u[5] += h2.y; u[6] += h2.z; u[7] += h2.w;
+    // every thread of every CTA of the cluster walks the same number of passes and reaches both barriers of each
+    for (int t0 = 0; t0 < N; t0 += NS) {
+        if (warp >= 2) {
+            // ---------------- accumulator columns [t0, t0 + NS) -> token-major staging tile
+            const int q = warp & 3;
+            const int row = q * 32 + lane;
+            for (int c0 = 0; c0 < NS; c0 += 16) {
+                uint32_t r[16];
+                if (ok) {
+                    tc_ld16(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(t0 + c0), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) stg[(size_t)(c0 + i) * TCK_LD + row] = ok ? __uint_as_float(r[i]) : 0.f;
             }
-            tc_finish<T>(a, n, first, v, u, pre[cnt]);
         }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        tc_cluster_sync();  // every CTA of the row block has staged its partial tile
+
+        if (warp >= 2 && t0 < a.n_tok) {
+            // ---------------- this CTA's share of the items: chunk c of 8 rows (8 pairs for SwiGLU) with c % KS == ks
+            const int et = tid - 64;
+            const int chunks = swiglu ? 8 : 16;
+            const int mine = (chunks - ks + KS - 1) / KS;  // chunks ks, ks + KS, ...
+            TcPre pre[8];
+            int cnt = 0;
+            for (int idx = et; idx < mine * NS; idx += 128, ++cnt) {
+                const int c = ks + (idx % mine) * KS, n = t0 + idx / mine;
+                const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                if (n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out)) tc_prefetch<T>(a, n, first, pre[cnt]);
+            }
+            cnt = 0;
+            for (int idx = et; idx < mine * NS; idx += 128, ++cnt) {
+                const int c = ks + (idx % mine) * KS, nl = idx / mine, n = t0 + nl;
+                const int first = swiglu ? rb * 64 + 8 * c : rb * TC_BM + 8 * c;
+                if (!(n < a.n_tok && first + 8 <= (swiglu ? a.di : a.out))) continue;
+                float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                const uint32_t sv = tc_smem(stg + (size_t)nl * TCK_LD + 8 * c);
+                for (int p = 0; p < KS; ++p) {
+                    const float4 lo = tc_ld_dsmem4(sv, (uint32_t)p), hi = tc_ld_dsmem4(sv + 16, (uint32_t)p);
+                    v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+                    v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+                    if (swiglu) {
+                        const float4 l2 = tc_ld_dsmem4(sv + 64 * 4, (uint32_t)p), h2 = tc_ld_dsmem4(sv + 64 * 4 + 16, (uint32_t)p);
+                        u[0] += l2.x; u[1] += l2.y; u[2] += l2.z; u[3] += l2.w;
+                        u[4] += h2.x; u[5] += h2.y; u[6] += h2.z; u[7] += h2.w;
+                    }
+                }
+                tc_finish<T>(a, n, first, v, u, pre[cnt]);
+            }
+        }
+        tc_cluster_sync();  // nobody overwrites or leaves while a peer may still read its tile
     }
-    tc_cluster_sync();  // nobody leaves while a peer may still read its tile
     p2p_signal(a.push);  // no-op without tensor parallelism
     __syncthreads();
     if (warp == 1) {
@@ -724,7 +735,7 @@ static size_t tc_smem_bytes(int N, int stages) {
 template <class T>
 static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = gemm_tc_kernel<T>;
-    const int N = a.n_tok <= 16 ? 16 : (a.n_tok <= 32 ? 32 : 64);
+    const int N = a.n_tok <= 16 ? 16 : (a.n_tok <= 32 ? 32 : (a.n_tok <= 64 ? 64 : (a.n_tok <= 128 ? 128 : 256)));
     int stages = 8;
     while (stages > 2 && tc_smem_bytes(N, stages) > (size_t)227 * 1024) --stages;
     const size_t smem = tc_smem_bytes(N, stages);
@@ -773,11 +784,14 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         const int n_rb_c = (n_pairs + 63) / 64, nkb_c = a.in / TC_BK;
         int KS = sms / n_rb_c;
         if (KS > 8) KS = 8;
+        if (KS < 1) KS = 1;
         while (KS > 1 && nkb_c / KS < 4) --KS;
-        const bool cluster_on = cluster_mode == 2 || (cluster_mode == 1 && (N == 64 || n_rb_c * 5 < sms));
-        if (vec && cluster_on && KS >= 2) {
+        // blocks of more than 64 tokens exist in this form only (clusters of one CTA where the matrix has row blocks to spare)
+        const bool cluster_on = N > 64 || cluster_mode == 2 || (cluster_mode == 1 && (N == 64 || n_rb_c * 5 < sms));
+        if (vec && cluster_on && (KS >= 2 || N > 64)) {
             const int stage_bytes = TC_A_BYTES + N * 128;
-            const size_t fixed = 1024 + (size_t)N * TCK_LD * 4 + sizeof(TcShared) + 64;
+            const int NS = N > 64 ? 64 : N;
+            const size_t fixed = 1024 + (size_t)NS * TCK_LD * 4 + sizeof(TcShared) + 64;
             int st = (int)(((size_t)227 * 1024 - fixed) / stage_bytes);
             if (st > TC_MAX_STAGES) st = TC_MAX_STAGES;
             const uint32_t idesc_c = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
@@ -799,6 +813,20 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
             g_linear_last_ctas = n_rb_c * KS;
             return LCU_OK;
         }
+    }
+    if (N > 64) {
+        // the 16-byte epilogue does not apply to this shape: 64-token passes of the general form
+        for (int t0 = 0; t0 < a.n_tok; t0 += 64) {
+            GemvArgs b = a;
+            b.n_tok = a.n_tok - t0 < 64 ? a.n_tok - t0 : 64;
+            b.x = reinterpret_cast<const unsigned char *>(a.x) + (size_t)t0 * a.stride_x * 2;
+            b.y = reinterpret_cast<unsigned char *>(a.y) + (size_t)t0 * a.stride_y * 2;
+            if (a.res) b.res = reinterpret_cast<const unsigned char *>(a.res) + (size_t)t0 * a.stride_res * 2;
+            if (a.pos) { b.pos = a.pos + t0; b.tok_seq = a.tok_seq + t0; }
+            int rc2 = tc_launch_t<T>(b, dt, s, pdl, dry);
+            if (rc2) return rc2;
+        }
+        return LCU_OK;
     }
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
     // Work split (stream-K): the (row block, K block) units are dealt to the SMs in equal contiguous ranges, so
@@ -825,7 +853,7 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
 }
 
 int gemm_tc_launch(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
-    LCU_REQUIRE(a.n_tok >= 1 && a.n_tok <= 64, "gemm_tc: n_tok = %d (1..64)", a.n_tok);
+    LCU_REQUIRE(a.n_tok >= 1 && a.n_tok <= 256, "gemm_tc: n_tok = %d (1..256)", a.n_tok);
     LCU_REQUIRE(dry || gemm_tc_supported(a.in, a.w_q8), "gemm_tc: in = %d unsupported", a.in);
     LCU_REQUIRE(a.out > 0 && a.out % 2 == 0, "gemm_tc: out = %d must be even", a.out);
     LCU_REQUIRE(a.prologue == PRO_NONE && !a.x_rows, "gemm_tc: takes prepared activations only");
