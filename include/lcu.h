@@ -155,6 +155,8 @@ LCU_API int lcu_seq_free(lcu_ctx *ctx, int seq);
  *               (used only by non-argmax requests; the reference draws it with rand::random)
  *   fast_map    n_fast pairs (index into the PREVIOUS round's out pairs, token slot): the
  *               slot's token is replaced on the device == `FastEmbedding` (op/fast_embedding.rs)
+ * Decode rounds (one token per request) replay a CUDA graph captured per (n_req, n_fast, sampling or not, out_dev): a
+ * host that rotates output buffers holds one graph per buffer; the table is cleared when it reaches 96 entries.
  * Under TP every rank calls this with the same arguments (the reference broadcasts them,
  * exec/group.rs:109-117); only rank 0 writes out_dev (the head itself is sharded over the ranks in
  * arg-max rounds of the peer-memory transport, see lcu_set_head_sharding). */

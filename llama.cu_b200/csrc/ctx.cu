@@ -1097,6 +1097,9 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
                             (int)((uintptr_t)out_dev >> 31), c->head_shard ? 1 : 0};
     auto it = c->graphs.find(key);
     if (it == c->graphs.end()) {
+        // A captured round is keyed by its shape AND by the output buffer (a host that rotates output buffers, as the
+        // reference's triple-buffered loop does, holds one graph per buffer): keep the table bounded
+        if (c->graphs.size() >= 96) drop_graphs(c);
         cudaGraph_t graph = nullptr;
         LCU_CHECK_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         int count = 0;
