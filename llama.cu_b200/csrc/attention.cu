@@ -404,6 +404,189 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     if (tid == 0) a.counters[(size_t)t * a.nkvh + hkv] = 0;  // ready for the next launch
 }
 
+// ------------------------------------------------------------------ prefill form
+// Rounds that hold prompts (several tokens of one sequence): a CTA owns a KV head and a GROUP of up to 64 / G
+// consecutive tokens of one sequence, i.e. 64 query rows (token, head) that all attend the same cached rows — the K/V
+// tile is gathered once per 64 queries instead of once per token.  Queries are the M side of both products (16 rows
+// per warp): S = Q.K^T with the query fragments held in registers for the whole kernel and K from the shared-memory
+// tile (ldmatrix), online softmax per row in registers (row maximum and sum across the four lanes of a quad),
+// probabilities rounded to the activation dtype and fed straight back as the A operand of P.V (no trip through shared
+// memory), V transposed by ldmatrix.  K and V tiles are double-buffered: the gather of tile t + 1 is in flight while
+// tile t is multiplied.  The causal limit is per row: a query at position p attends positions [0, p].  Same
+// arithmetic contract as the decode form (f32 scores and softmax, rounded probabilities, row sum over the rounded
+// values, one rounding of the output); no split-KV — a prefill round has CTAs to spare.
+struct AttnGroup {
+    int first, count;  // index of the group's first token in the round, tokens in the group (<= 64 / G)
+};
+constexpr int ATT_MAX_PAGES = 512;  // page ids of one sequence held in shared memory
+
+template <class T, int DH, int G>
+__global__ void __launch_bounds__(ATT_THREADS) attn_prefill_kernel(const AttnArgs a, const AttnGroup *__restrict__ groups) {
+    constexpr int ROW = DH + 8;      // padded K/V row (elements)
+    constexpr int CH = DH / 8;       // 16-byte chunks per row
+    constexpr int KSTEPS = DH / 16;  // k-steps of the score product
+    constexpr int NTS = ATT_TILE / 8;  // 8-wide score tiles per K tile
+    constexpr int NTO = DH / 8;        // 8-wide output tiles
+    extern __shared__ __align__(16) unsigned char smem[];
+    T *Ks = reinterpret_cast<T *>(smem);      // [2][TILE][ROW]
+    T *Vs = Ks + 2 * ATT_TILE * ROW;          // [2][TILE][ROW]
+    __shared__ int pg[ATT_MAX_PAGES];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, t4 = lane & 3;
+    const int hkv = blockIdx.x;
+    const AttnGroup grp = groups[blockIdx.y];
+    const T *kv_pool = reinterpret_cast<const T *>(a.kv_pool);
+
+    const int pos0 = (int)a.tok_pos[grp.first];           // position of the group's first token
+    const int ctx = pos0 + grp.count;                     // rows the group's last token attends
+    const int seq = a.tok_seq[grp.first];
+    const int n_tiles = (ctx + ATT_TILE - 1) / ATT_TILE;
+    const int n_pages = (ctx + a.geom.page_tokens - 1) >> a.geom.page_shift;
+    for (int i = tid; i < n_pages; i += ATT_THREADS) pg[i] = a.page_table[(size_t)seq * a.pt_stride + i];
+    grid_dep_wait();
+
+    // this thread's two query rows: r0 = 16 warp + gid, r1 = r0 + 8; row r = (token r / G, head r % G)
+    const int r0 = warp * 16 + gid, r1 = r0 + 8;
+    const int tt0 = r0 / G, tt1 = r1 / G;
+    const bool v0 = tt0 < grp.count, v1 = tt1 < grp.count;
+    const int lim0 = v0 ? pos0 + tt0 : -1, lim1 = v1 ? pos0 + tt1 : -1;  // last position each row attends
+    uint32_t qa[KSTEPS][4];
+    {
+        const T *q0 = reinterpret_cast<const T *>(a.q) + (size_t)(grp.first + (v0 ? tt0 : 0)) * a.stride_q + (size_t)(hkv * G + r0 % G) * DH;
+        const T *q1 = reinterpret_cast<const T *>(a.q) + (size_t)(grp.first + (v1 ? tt1 : 0)) * a.stride_q + (size_t)(hkv * G + r1 % G) * DH;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qa[ks][0] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 2 * t4) : 0u;
+            qa[ks][1] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 2 * t4) : 0u;
+            qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t *>(q0 + ks * 16 + 8 + 2 * t4) : 0u;
+            qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t *>(q1 + ks * 16 + 8 + 2 * t4) : 0u;
+        }
+    }
+    const size_t blk = (size_t)a.geom.page_tokens * DH;
+    const size_t kbase = ((size_t)(a.layer * 2) * a.geom.nkvh + hkv) * blk;
+    const size_t voff = (size_t)a.geom.nkvh * blk;
+    const int lcol8 = (tid % CH) * 8, j0 = tid / CH;
+    auto load_tile = [&](int tile, int buf) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            T *dst = (which ? Vs : Ks) + (size_t)buf * ATT_TILE * ROW;
+#pragma unroll
+            for (int i = 0; i < (ATT_TILE * CH) / ATT_THREADS; ++i) {
+                const int j = j0 + (ATT_THREADS / CH) * i;
+                const int pos = tile * ATT_TILE + j;
+                const bool valid = pos < ctx;
+                const int page = valid ? pg[pos >> a.geom.page_shift] : 0;
+                const int slot = pos & (a.geom.page_tokens - 1);
+                const T *src = kv_pool + (valid ? (size_t)page * a.geom.page_elems + kbase + (which ? voff : 0) + (size_t)slot * DH + lcol8 : 0);
+                cp_async_16(dst + j * ROW + lcol8, src, valid);
+            }
+        }
+    };
+    __syncthreads();  // page ids staged
+    load_tile(0, 0);
+    cp_async_commit();
+
+    const float scale = 1.0f / sqrtf((float)DH);
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[NTO][4];
+#pragma unroll
+    for (int i = 0; i < NTO; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const int buf = tile & 1;
+        if (tile + 1 < n_tiles) load_tile(tile + 1, buf ^ 1);  // the other buffer was released by the barrier below
+        cp_async_commit();
+        cp_async_wait<1>();  // tile `tile` has landed
+        __syncthreads();
+        const T *Kt = Ks + (size_t)buf * ATT_TILE * ROW, *Vt = Vs + (size_t)buf * ATT_TILE * ROW;
+
+        // ---- scores of this warp's 16 query rows against the 64 positions of the tile
+        float sc[NTS][4];
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < NTS / 2; ++np) {
+                uint32_t kb[4];  // K fragments of score tiles 2 np and 2 np + 1
+                ldmatrix_x4(kb, Kt + (size_t)(np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * ROW + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma16816<T>(sc[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
+                mma16816<T>(sc[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[2], kb[3]);
+            }
+        }
+        // ---- causal mask, online softmax per row
+        float mt0 = -INFINITY, mt1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt) {
+            const int p = tile * ATT_TILE + nt * 8 + 2 * t4;
+            sc[nt][0] = p <= lim0 ? sc[nt][0] * scale : -INFINITY;
+            sc[nt][1] = p + 1 <= lim0 ? sc[nt][1] * scale : -INFINITY;
+            sc[nt][2] = p <= lim1 ? sc[nt][2] * scale : -INFINITY;
+            sc[nt][3] = p + 1 <= lim1 ? sc[nt][3] * scale : -INFINITY;
+            mt0 = fmaxf(mt0, fmaxf(sc[nt][0], sc[nt][1]));
+            mt1 = fmaxf(mt1, fmaxf(sc[nt][2], sc[nt][3]));
+        }
+        mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
+        mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
+        const float mn0 = fmaxf(m0, mt0), mn1 = fmaxf(m1, mt1);
+        const float c0 = m0 == -INFINITY ? 0.f : expf(m0 - mn0), c1 = m1 == -INFINITY ? 0.f : expf(m1 - mn1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;  // a fully masked row stays at zero
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pa[NTS][2];  // probabilities rounded to the activation dtype: rows r0 (pa[.][0]) and r1 (pa[.][1])
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NTS; ++nt) {
+            const T p00 = Act<T>::from_f(expf(sc[nt][0] - mu0)), p01 = Act<T>::from_f(expf(sc[nt][1] - mu0));
+            const T p10 = Act<T>::from_f(expf(sc[nt][2] - mu1)), p11 = Act<T>::from_f(expf(sc[nt][3] - mu1));
+            s0 += Act<T>::to_f(p00) + Act<T>::to_f(p01);
+            s1 += Act<T>::to_f(p10) + Act<T>::to_f(p11);
+            pa[nt][0] = Act<T>::pack(Act<T>::to_f(p00), Act<T>::to_f(p01));
+            pa[nt][1] = Act<T>::pack(Act<T>::to_f(p10), Act<T>::to_f(p11));
+        }
+        l0 = l0 * c0 + s0;  // per-thread partial sums: the four lanes of a quad are added at the end
+        l1 = l1 * c1 + s1;
+#pragma unroll
+        for (int i = 0; i < NTO; ++i) {
+            o[i][0] *= c0; o[i][1] *= c0;
+            o[i][2] *= c1; o[i][3] *= c1;
+        }
+        // ---- O += P . V: k-step kk covers positions [16 kk, 16 kk + 16) = score tiles 2 kk, 2 kk + 1
+#pragma unroll
+        for (int kk = 0; kk < ATT_TILE / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < NTO / 2; ++dp) {
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, Vt + (size_t)(kk * 16 + (lane & 15)) * ROW + dp * 16 + (lane >> 4) * 8);
+                mma16816<T>(o[2 * dp], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], vb[0], vb[1]);
+                mma16816<T>(o[2 * dp + 1], pa[2 * kk][0], pa[2 * kk][1], pa[2 * kk + 1][0], pa[2 * kk + 1][1], vb[2], vb[3]);
+            }
+        }
+        __syncthreads();  // everyone is done with buffer `buf`: the next iteration's gather may overwrite it
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    T *out = reinterpret_cast<T *>(a.o);
+    if (v0) {
+        const float inv = 1.f / l0;
+        T *dst = out + (size_t)(grp.first + tt0) * a.stride_o + (size_t)(hkv * G + r0 % G) * DH + 2 * t4;
+#pragma unroll
+        for (int i = 0; i < NTO; ++i) *reinterpret_cast<uint32_t *>(dst + 8 * i) = Act<T>::pack(o[i][0] * inv, o[i][1] * inv);
+    }
+    if (v1) {
+        const float inv = 1.f / l1;
+        T *dst = out + (size_t)(grp.first + tt1) * a.stride_o + (size_t)(hkv * G + r1 % G) * DH + 2 * t4;
+#pragma unroll
+        for (int i = 0; i < NTO; ++i) *reinterpret_cast<uint32_t *>(dst + 8 * i) = Act<T>::pack(o[i][2] * inv, o[i][3] * inv);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -492,6 +675,56 @@ int attn_launch(const AttnArgs &a, int dt, cudaStream_t s, bool pdl, bool dry) {
     if (dt == LCU_F16) return a.dh == 64 ? attn_dh<__half, 64>(a, s, pdl, dry) : attn_dh<__half, 128>(a, s, pdl, dry);
     if (dt == LCU_BF16)
         return a.dh == 64 ? attn_dh<__nv_bfloat16, 64>(a, s, pdl, dry) : attn_dh<__nv_bfloat16, 128>(a, s, pdl, dry);
+    set_error("attention: activation dtype %d unsupported", dt);
+    return LCU_ERR_INVALID;
+}
+
+
+// ---- prefill form
+template <class T, int DH, int G>
+static int attn_prefill_inst(const AttnArgs &a, const void *groups, int n_groups, cudaStream_t s, bool dry) {
+    auto kernel = attn_prefill_kernel<T, DH, G>;
+    const size_t smem = (size_t)4 * ATT_TILE * (DH + 8) * sizeof(T);
+    static std::mutex mu;
+    static std::map<int, bool> done;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done[dev]) {
+            if (smem > 48 * 1024) LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done[dev] = true;
+        }
+    }
+    if (dry) return LCU_OK;
+    LCU_CHECK_CUDA(launch_kernel(kernel, dim3(a.nkvh, n_groups), dim3(ATT_THREADS), smem, s, false, a,
+                                 reinterpret_cast<const AttnGroup *>(groups)));
+    return LCU_OK;
+}
+
+template <class T, int DH>
+static int attn_prefill_dh(const AttnArgs &a, const void *groups, int n_groups, cudaStream_t s, bool dry) {
+    switch (a.nh / a.nkvh) {
+    case 1: return attn_prefill_inst<T, DH, 1>(a, groups, n_groups, s, dry);
+    case 2: return attn_prefill_inst<T, DH, 2>(a, groups, n_groups, s, dry);
+    case 4: return attn_prefill_inst<T, DH, 4>(a, groups, n_groups, s, dry);
+    case 8: return attn_prefill_inst<T, DH, 8>(a, groups, n_groups, s, dry);
+    default: set_error("attention: nh/nkvh = %d unsupported (1, 2, 4, 8)", a.nh / a.nkvh); return LCU_ERR_INVALID;
+    }
+}
+
+int attn_prefill_group_tokens(int nh, int nkvh) { return ATT_TILE / (nh / nkvh); }
+bool attn_prefill_supported(int pt_stride) { return pt_stride <= ATT_MAX_PAGES; }
+
+int attn_prefill_launch(const AttnArgs &a, const void *groups_dev, int n_groups, int dt, cudaStream_t s, bool dry) {
+    if (n_groups <= 0 && !dry) return LCU_OK;
+    LCU_REQUIRE(a.nkvh > 0 && a.nh % a.nkvh == 0, "attention: nh = %d is not a multiple of nkvh = %d", a.nh, a.nkvh);
+    LCU_REQUIRE(a.dh == 64 || a.dh == 128, "attention: dh = %d unsupported (64, 128)", a.dh);
+    LCU_REQUIRE(dry || (a.kv_pool && groups_dev && a.pt_stride <= ATT_MAX_PAGES), "attention (prefill form): needs the paged cache, groups and at most %d pages per sequence", ATT_MAX_PAGES);
+    if (dt == LCU_F16) return a.dh == 64 ? attn_prefill_dh<__half, 64>(a, groups_dev, n_groups, s, dry) : attn_prefill_dh<__half, 128>(a, groups_dev, n_groups, s, dry);
+    if (dt == LCU_BF16)
+        return a.dh == 64 ? attn_prefill_dh<__nv_bfloat16, 64>(a, groups_dev, n_groups, s, dry)
+                          : attn_prefill_dh<__nv_bfloat16, 128>(a, groups_dev, n_groups, s, dry);
     set_error("attention: activation dtype %d unsupported", dt);
     return LCU_ERR_INVALID;
 }

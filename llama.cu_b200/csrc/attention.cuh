@@ -47,6 +47,13 @@ void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok);
 // dry: only prepare the kernel variant (shared-memory attribute), launch nothing.
 int attn_launch(const AttnArgs &a, int dt, cudaStream_t s, bool pdl, bool dry = false);
 
+// Prefill form: one CTA per (KV head, group of up to attn_prefill_group_tokens consecutive tokens of ONE sequence);
+// groups_dev: n_groups pairs (index of the first token in the round, tokens in the group).  Paged cache only, no
+// split-KV; needs pt_stride <= 512 (attn_prefill_supported).
+int attn_prefill_group_tokens(int nh, int nkvh);
+bool attn_prefill_supported(int pt_stride);
+int attn_prefill_launch(const AttnArgs &a, const void *groups_dev, int n_groups, int dt, cudaStream_t s, bool dry = false);
+
 // Appends k, v [seq, nkvh, dh] (strided) to linear caches at pos.. (the write half of
 // operators::attention_kv_cached as called from llama.cu/src/exec/step.rs:162-182).
 int kv_append_linear(void *k_cache, int stkc, int shkc, void *v_cache, int stvc, int shvc, const void *k, int stk,

@@ -137,7 +137,7 @@ struct lcu_ctx {
 
 // offsets of the sections of a round descriptor (all 16-byte aligned)
 struct DescLayout {
-    size_t tokens, pos, tok_req, out_idx, fast_map, args, randoms, page_table, total;
+    size_t tokens, pos, tok_req, out_idx, fast_map, args, randoms, page_table, groups, total;
 };
 static DescLayout desc_layout(int n_tok, int n_req, int pt_stride) {
     DescLayout L;
@@ -151,6 +151,7 @@ static DescLayout desc_layout(int n_tok, int n_req, int pt_stride) {
     L.args = take((size_t)n_req * sizeof(lcu_sample_args));
     L.randoms = take((size_t)n_req * 4);
     L.page_table = take((size_t)n_req * pt_stride * 4);
+    L.groups = take((size_t)n_tok * 8);  // token groups of the prefill form of attention (at most one per token)
     L.total = o;
     return L;
 }
@@ -397,6 +398,7 @@ int lcu_ctx_create(const lcu_model_desc *desc, int device, int tp_rank, int tp_s
             AttnArgs a{};
             a.n_tok = 1; a.nh = c->nh_l; a.nkvh = c->nkvh_l; a.dh = d.dh; a.n_splits = 1;
             rc = attn_launch(a, c->dt, nullptr, false, true);
+            if (!rc) rc = attn_prefill_launch(a, nullptr, 0, c->dt, nullptr, true);
         }
         if (rc) {
             lcu_ctx_destroy(c);
@@ -645,6 +647,7 @@ namespace {
 
 struct Round {
     int n_tok, n_req, n_fast;
+    int n_groups;  // token groups for the prefill form of attention (0: decode form)
     bool any_sampling;
     bool decode_only;  // one new token per sequence
     DescLayout L;
@@ -817,7 +820,9 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             const bool attn_pdl = pdl || (!batched && (pdl_edges & 1));
             a.early_kv = (attn_pdl && r.decode_only) ? 1 : 0;
             a.pdl_trigger = 1;
-            rc = attn_launch(a, dt, s, attn_pdl);
+            // rounds that hold prompts: 64 query rows per CTA share every K/V tile (prefill form)
+            if (r.n_groups > 0) rc = attn_prefill_launch(a, D + r.L.groups, r.n_groups, dt, s);
+            else rc = attn_launch(a, dt, s, attn_pdl);
             if (rc) return rc;
             ++launches;
         }
@@ -1056,6 +1061,21 @@ extern "C" int lcu_step(lcu_ctx *c, lcu_stream_t stream, int n_req, const lcu_re
             ho[i] = (uint32_t)(t - 1);  // out_idx() with out == 1, exec/engine.rs:360-371
             const SeqState &sq = c->seqs[reqs[i].seq];
             for (size_t pg = 0; pg < sq.pages.size(); ++pg) ht[(size_t)i * c->pt_stride + pg] = sq.pages[pg];
+        }
+        // prompts in the round: consecutive tokens of a request are grouped for the prefill form of attention
+        r.n_groups = 0;
+        if (!decode_only && attn_prefill_supported(c->pt_stride)) {
+            int32_t *hg = reinterpret_cast<int32_t *>(H + r.L.groups);
+            const int gt = attn_prefill_group_tokens(c->nh_l, c->nkvh_l);
+            int t0 = 0;
+            for (int i = 0; i < n_req; ++i) {
+                for (uint32_t j = 0; j < reqs[i].len; j += gt) {
+                    hg[2 * r.n_groups] = t0 + (int)j;
+                    hg[2 * r.n_groups + 1] = (int)(reqs[i].len - j < (uint32_t)gt ? reqs[i].len - j : gt);
+                    ++r.n_groups;
+                }
+                t0 += (int)reqs[i].len;
+            }
         }
         if (n_fast) memcpy(H + r.L.fast_map, fast_map, (size_t)n_fast * 8);
         lcu_sample_args *ha = reinterpret_cast<lcu_sample_args *>(H + r.L.args);
