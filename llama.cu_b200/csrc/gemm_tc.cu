@@ -787,7 +787,10 @@ static int tc_launch_t(const GemvArgs &a, int dt, cudaStream_t s, bool pdl, bool
         if (KS < 1) KS = 1;
         while (KS > 1 && nkb_c / KS < 4) --KS;
         // blocks of more than 64 tokens exist in this form only (clusters of one CTA where the matrix has row blocks to spare)
-        const bool cluster_on = N > 64 || cluster_mode == 2 || (cluster_mode == 1 && (N == 64 || n_rb_c * 5 < sms));
+        // 1: where it measured faster than the stream-K split: 64-token blocks, and matrices whose row blocks leave room
+        // for clusters of four and more (8B batch 32, per launch: O 20.9 -> 18.3 us, down 35.4 -> 32.9 us; the 48-row-block
+        // QKV matrix with clusters of three 26.8 -> 34.5 us, so it stays on stream-K)
+        const bool cluster_on = N > 64 || cluster_mode == 2 || (cluster_mode == 1 && (N == 64 || n_rb_c * 4 <= sms));
         if (vec && cluster_on && (KS >= 2 || N > 64)) {
             const int stage_bytes = TC_A_BYTES + N * 128;
             const int NS = N > 64 ? 64 : N;
