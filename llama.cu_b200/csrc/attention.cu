@@ -63,17 +63,16 @@ __device__ __forceinline__ uint32_t att_map_peer(const void *local, uint32_t cta
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(cta));
     return ra;
 }
-__device__ __forceinline__ float att_ld_peer(uint32_t ra) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-    return v;
+__device__ __forceinline__ void att_st_peer2(uint32_t ra, float x, float y) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1,%2};" ::"r"(ra), "f"(x), "f"(y) : "memory");
 }
-__device__ __forceinline__ float2 att_ld_peer2(uint32_t ra) {
-    float2 v;
-    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(ra) : "memory");
-    return v;
+// Bytes of the decode kernel's shared memory in front of the cluster-merge region (K, V, probabilities, scores and
+// the running softmax state), rounded up to 16.
+template <class T, int DH, int G>
+__host__ __device__ constexpr size_t att_merge_offset() {
+    return ((size_t)2 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)16 * (ATT_TILE + 8) * sizeof(T) +
+            (size_t)(G * ATT_TILE + 3 * G) * sizeof(float) + 15) / 16 * 16;
 }
-
 // Both products run on tensor cores (mma.sync m16n8k16, f32 accumulation):
 //   scores  S[pos][head] = K[pos][:] . q[head][:]   M = 16 positions per warp, N = 8 head slots (G used), K = dh
 //   output  O[head][d]   = P[head][:] . V[:][d]     M = 16 head slots (G used), N = dh / 4 per warp, K = 64 positions
@@ -96,6 +95,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     float *corr = S + G * ATT_TILE;                      // [G]
     float *m_run = corr + G;                             // [G]
     float *l_run = m_run + G;                            // [G]
+    // cluster merge only: every split's unnormalised partial [z][G][DH] and (max, sum) [z][G][2], filled in the FIRST
+    // split's shared memory by its peers
+    float *mrg_o = reinterpret_cast<float *>(smem + att_merge_offset<T, DH, G>());
+    float *mrg_ml = mrg_o + (size_t)a.cluster_z * G * DH;
     __shared__ int is_last;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -115,10 +118,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     // shared memory; CTAs without work still take part in its two barriers
     const bool clus = a.cluster_z > 0;
     if (sp >= my_splits) {
-        if (clus) {
-            att_cluster_sync();
-            att_cluster_sync();
-        }
+        if (clus) att_cluster_sync();
         return;  // leaving counts as releasing the dependents
     }
     if (a.pdl_trigger == 0) grid_dep_launch();
@@ -305,46 +305,47 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     const int d0 = warp * DW + 2 * t4;
     T *og = reinterpret_cast<T *>(a.o) + (size_t)t * a.stride_o + (size_t)hkv * G * DH;
     if (clus) {
-        // unnormalised partial into this CTA's shared memory (the K buffer is free now); m_run / l_run are there already
-        float *Os = reinterpret_cast<float *>(Ks);  // [G][DH]
-        if (my_splits > 1 && gid < G) {
+        // every split stores its unnormalised partial and (max, sum) into the FIRST split's shared memory (remote
+        // stores through the cluster's distributed shared memory), one barrier publishes them, and the first split
+        // merges from its own shared memory; nobody reads a peer's memory, so the peers leave after the barrier
+        if (my_splits > 1) {
+            if (gid < G) {
+                const uint32_t ob = att_map_peer(mrg_o + ((size_t)sp * G + gid) * DH + d0, 0u);
 #pragma unroll
-            for (int i = 0; i < NT; ++i) *reinterpret_cast<float2 *>(Os + gid * DH + d0 + 8 * i) = make_float2(acc[i][0], acc[i][1]);
+                for (int i = 0; i < NT; ++i) att_st_peer2(ob + 32 * i, acc[i][0], acc[i][1]);
+            }
+            if (tid < G) att_st_peer2(att_map_peer(mrg_ml + ((size_t)sp * G + tid) * 2, 0u), m_run[tid], l_run[tid]);
         }
-        __syncthreads();
         att_cluster_sync();
-        if (sp == 0 && gid < G) {
-            if (my_splits == 1) {
-                const float inv = 1.f / l_run[gid];
+        if (sp != 0 || gid >= G) return;
+        if (my_splits == 1) {
+            const float inv = 1.f / l_run[gid];
 #pragma unroll
-                for (int i = 0; i < NT; ++i)
-                    *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(acc[i][0] * inv, acc[i][1] * inv);
-            } else {
-                float M = -INFINITY;
-                for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, att_ld_peer(att_map_peer(m_run + gid, (uint32_t)s2)));
-                float L = 0.f, O[NT][2];
+            for (int i = 0; i < NT; ++i)
+                *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(acc[i][0] * inv, acc[i][1] * inv);
+            return;
+        }
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < my_splits; ++s2) M = fmaxf(M, mrg_ml[((size_t)s2 * G + gid) * 2]);
+        float L = 0.f, O[NT][2];
 #pragma unroll
-                for (int i = 0; i < NT; ++i) O[i][0] = O[i][1] = 0.f;
-                for (int s2 = 0; s2 < my_splits; ++s2) {
-                    const float ms = att_ld_peer(att_map_peer(m_run + gid, (uint32_t)s2));
-                    const float ls = att_ld_peer(att_map_peer(l_run + gid, (uint32_t)s2));
-                    const float w = ms == -INFINITY ? 0.f : expf(ms - M);
-                    L = fmaf(ls, w, L);
-                    const uint32_t ob = att_map_peer(Os + gid * DH + d0, (uint32_t)s2);
+        for (int i = 0; i < NT; ++i) O[i][0] = O[i][1] = 0.f;
+        for (int s2 = 0; s2 < my_splits; ++s2) {
+            const float ms = mrg_ml[((size_t)s2 * G + gid) * 2], ls = mrg_ml[((size_t)s2 * G + gid) * 2 + 1];
+            const float w = ms == -INFINITY ? 0.f : expf(ms - M);
+            L = fmaf(ls, w, L);
+            const float *ob = mrg_o + ((size_t)s2 * G + gid) * DH + d0;
 #pragma unroll
-                    for (int i = 0; i < NT; ++i) {
-                        const float2 o = att_ld_peer2(ob + 32 * i);
-                        O[i][0] = fmaf(o.x, w, O[i][0]);
-                        O[i][1] = fmaf(o.y, w, O[i][1]);
-                    }
-                }
-                const float inv = 1.f / L;
-#pragma unroll
-                for (int i = 0; i < NT; ++i)
-                    *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(O[i][0] * inv, O[i][1] * inv);
+            for (int i = 0; i < NT; ++i) {
+                const float2 o = *reinterpret_cast<const float2 *>(ob + 8 * i);
+                O[i][0] = fmaf(o.x, w, O[i][0]);
+                O[i][1] = fmaf(o.y, w, O[i][1]);
             }
         }
-        att_cluster_sync();  // nobody leaves while the first split may still read its partial
+        const float inv = 1.f / L;
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+            *reinterpret_cast<uint32_t *>(og + gid * DH + d0 + 8 * i) = Act<T>::pack(O[i][0] * inv, O[i][1] * inv);
         return;
     }
     if (my_splits == 1) {
@@ -611,8 +612,9 @@ void attn_bind_scratch(AttnArgs &a, void *scratch, int max_tok) {
 template <class T, int DH, int G>
 static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     auto kernel = attn_kernel<T, DH, G>;
-    size_t smem = (size_t)2 * ATT_TILE * (DH + 8) * sizeof(T) + (size_t)16 * (ATT_TILE + 8) * sizeof(T) +
-                  (size_t)(G * ATT_TILE + 3 * G) * sizeof(float);
+    // a cluster launch adds the merge region: [z][G][DH] partials and [z][G][2] (max, sum)
+    const size_t smem_max = att_merge_offset<T, DH, G>() + (size_t)8 * G * (DH + 2) * sizeof(float);
+    size_t smem = att_merge_offset<T, DH, G>() + (size_t)(a.cluster_z > 0 ? a.cluster_z : 0) * G * (DH + 2) * sizeof(float);
     static std::mutex mu;
     static std::map<int, bool> done;
     int dev = 0;
@@ -620,7 +622,7 @@ static int attn_inst(const AttnArgs &a, cudaStream_t s, bool pdl, bool dry) {
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!done[dev]) {
-            if (smem > 48 * 1024) LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            if (smem_max > 48 * 1024) LCU_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
             done[dev] = true;
         }
     }

@@ -595,6 +595,7 @@ int lcu_set_tuning(lcu_ctx *c, const char *key, long long value) {
     if (k == "pdl_edges") t.pdl_edges = (int)value;
     else if (k == "gemv_ctas_per_sm") { LCU_REQUIRE(value >= 1 && value <= 2, "set_tuning: gemv_ctas_per_sm = %lld (1, 2)", value); t.gemv_ctas_per_sm = (int)value; }
     else if (k == "q8_rows") { LCU_REQUIRE(value == 1 || value == 2 || value == 4, "set_tuning: q8_rows = %lld (1, 2, 4)", value); t.q8_rows = (int)value; }
+    else if (k == "gemv_lean_norm") t.gemv_lean_norm = value != 0;
     else if (k == "tc") t.tc = value != 0;
     else if (k == "tc_block") { LCU_REQUIRE(value == 64 || value == 128 || value == 256, "set_tuning: tc_block = %lld (64, 128, 256)", value); t.tc_block = (int)value; }
     else if (k == "tc_cluster") { LCU_REQUIRE(value >= 0 && value <= 2, "set_tuning: tc_cluster = %lld (0..2)", value); t.tc_cluster = (int)value; }

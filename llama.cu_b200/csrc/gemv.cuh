@@ -46,6 +46,7 @@ struct GemvArgs {
     // tuning: 0 = trigger dependents at kernel start, 1 = after the main loop, 2 = never (implicit at exit)
     int pdl_trigger;
     int early_prefetch;  // 1 = first weight loads before griddepcontrol.wait
+    int lean_norm;       // one token: RMSNorm prologue from registers (norm weights fetched before the wait)
     // tensor parallelism: EPI_STORE / EPI_RESIDUAL outputs go to every rank's all-reduce slot instead of y
     P2pPush push;
 };
