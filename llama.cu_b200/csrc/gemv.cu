@@ -45,7 +45,9 @@ __device__ __forceinline__ void vec8_to_f32(const uint4 &v, float f[8]) {
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
 
-template <class T, bool Q8, int NT, int KI, int RP>
+// PRO: 0 = activations staged as they are, 1 = RMSNorm (any token count, f32 or 16-bit norm weights), 2 = RMSNorm of one
+// token from registers
+template <class T, bool Q8, int NT, int KI, int RP, int PRO>
 __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(const GemvArgs a, int KS, int RS, int n_pairs) {
     constexpr int R = 2 * RP;
     constexpr int VE = Q8 ? 16 : 8;  // weights per 16-byte vector
@@ -102,9 +104,9 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
     // shared memory once -- two barriers and one L2 round trip after the wait instead of four and two.  Same summation
     // order and the same products as the general path below.
     const int nv8 = a.in / 8;
-    const bool lean = NT == 1 && a.prologue == PRO_RMSNORM && !a.norm_f32 && a.lean_norm && nv8 <= 2 * (int)blockDim.x;
+    constexpr bool lean = PRO == 2;
     uint4 nwv[2];
-    if (lean) {
+    if constexpr (lean) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
     grid_dep_wait();
     if (a.early_prefetch == 0 && n_groups > 0) load_group(0);
 
-    if (lean) {
+    if constexpr (lean) {
         const size_t row = a.x_rows ? a.x_rows[0] : 0;
         const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.x) + row * a.stride_x);
         uint4 xv[2];
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        if (a.prologue == PRO_RMSNORM) {
+        if constexpr (PRO == 1) {
             float ss[NT];
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
@@ -375,9 +377,9 @@ static GemvPlan plan_for(int in, bool q8, int nt) {
     return best;
 }
 
-template <class T, bool Q8, int NT, int KI, int RP>
+template <class T, bool Q8, int NT, int KI, int RP, int PRO>
 static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
-    auto kernel = gemv_kernel<T, Q8, NT, KI, RP>;
+    auto kernel = gemv_kernel<T, Q8, NT, KI, RP, PRO>;
     // activations + double-buffered per-warp partial sums (also the RMSNorm scratch)
     size_t smem = (size_t)NT * a.in * sizeof(T) + (size_t)2 * 16 * (2 * RP * NT) * sizeof(float);
     int block = pl.nwarps * 32;
@@ -424,8 +426,14 @@ static int launch_inst(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaS
 
 template <class T, bool Q8, int NT>
 static int launch_nt(const GemvArgs &a, const GemvPlan &pl, int n_pairs, cudaStream_t s, bool pdl, bool dry) {
-#define LCU_GEMV_CASE(KI_, RP_) \
-    if (pl.KI == KI_ && pl.RP == RP_) return launch_inst<T, Q8, NT, KI_, RP_>(a, pl, n_pairs, s, pdl, dry);
+    // prologue variant: the one-token register form needs 16-bit norm weights and at most two vectors per thread
+    const int pro = a.prologue != PRO_RMSNORM ? 0 : ((NT == 1 && !a.norm_f32 && a.lean_norm && a.in / 8 <= 2 * pl.nwarps * 32) ? 2 : 1);
+#define LCU_GEMV_CASE(KI_, RP_)                                                                                   \
+    if (pl.KI == KI_ && pl.RP == RP_) {                                                                           \
+        if (pro == 0) return launch_inst<T, Q8, NT, KI_, RP_, 0>(a, pl, n_pairs, s, pdl, dry);                    \
+        if (pro == 1) return launch_inst<T, Q8, NT, KI_, RP_, 1>(a, pl, n_pairs, s, pdl, dry);                    \
+        if constexpr (NT == 1) return launch_inst<T, Q8, NT, KI_, RP_, 2>(a, pl, n_pairs, s, pdl, dry);           \
+    }
     if constexpr (Q8) {
         LCU_GEMV_CASE(1, 4) LCU_GEMV_CASE(1, 2) LCU_GEMV_CASE(2, 2) LCU_GEMV_CASE(4, 1) LCU_GEMV_CASE(8, 1)
     } else if constexpr (NT == 1) {
@@ -489,8 +497,13 @@ int gemv_warm(int in, int out, bool q8, int dt) {
     for (int nt = 1; nt <= gemv_max_tokens(in); nt *= 2) {
         GemvArgs a{};
         a.in = in; a.out = out; a.n_tok = nt; a.w_q8 = q8; a.stride_x = in; a.epilogue = EPI_STORE;
-        int rc = gemv_launch(a, dt, nullptr, false, true);
-        if (rc) return rc;
+        // every prologue variant: none, RMSNorm with 16-bit and with f32 norm weights
+        for (int v = 0; v < 3; ++v) {
+            a.prologue = v == 0 ? PRO_NONE : PRO_RMSNORM;
+            a.norm_f32 = v == 2;
+            int rc = gemv_launch(a, dt, nullptr, false, true);
+            if (rc) return rc;
+        }
     }
     return LCU_OK;
 }
