@@ -99,6 +99,24 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
     // while those weights are in flight.  early_prefetch == 3 keeps the older order (weights, then activations).
     const bool x_first = a.early_prefetch == 1;
     if (a.early_prefetch == 3 && n_groups > 0) load_group(0);
+    // RoPE / KV-append epilogue: position, cache page and the sin / cos rows of every token come from the round's
+    // descriptor and constant tables, not from the predecessor -- staged in shared memory here, before the dependency
+    // wait, so that the epilogues of the row groups (and the kernel's tail) hold no chain of global loads
+    __shared__ RopeStage rope_stage;
+    const bool rope_staged = a.epilogue == EPI_ROPE_KV && a.dh <= 128;
+    if (rope_staged) {
+        const int half_dh = a.dh >> 1;
+        for (int i = threadIdx.x; i < a.n_tok * half_dh; i += blockDim.x) {
+            const int t = i / half_dh, e = i - t * half_dh;
+            const uint32_t p = a.pos[t];
+            rope_stage.sn[t][e] = a.sin_t[(size_t)p * half_dh + e];
+            rope_stage.cs[t][e] = a.cos_t[(size_t)p * half_dh + e];
+            if (e == 0) {
+                rope_stage.pos[t] = p;
+                rope_stage.page[t] = a.page_table[(size_t)a.tok_seq[t] * a.pt_stride + (p >> a.geom.page_shift)];
+            }
+        }
+    }
     // One token, RMSNorm, at most two vectors per thread: the norm weights are constants and are fetched BEFORE the
     // dependency wait, the activations go from global memory straight to registers, are squared, scaled and written to
     // shared memory once -- two barriers and one L2 round trip after the wait instead of four and two.  Same summation
@@ -236,6 +254,17 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
 
     // ---- main loop over row groups
     for (int g = 0; g < n_groups; ++g) {
+        // the finishing lanes ask for their residual pair now: it arrives while the group is multiplied and reduced
+        EpiPre pre;
+        if (rope_staged) pre.rope = &rope_stage;
+        if (a.epilogue == EPI_RESIDUAL && ks == 0 && rs < RS && lane < RP * NT) {
+            const int rp = lane / NT, t = lane - rp * NT;
+            const int p = p_begin + g * group_pairs + rs * RP + rp;
+            if (p < p_end && t < a.n_tok) {
+                pre.res = *reinterpret_cast<const uint32_t *>(reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + (size_t)p * 2);
+                pre.has_res = true;
+            }
+        }
         float acc[R][NT];
 #pragma unroll
         for (int r = 0; r < R; ++r)
@@ -329,7 +358,7 @@ __global__ void __launch_bounds__(512, (NT == 1 && !Q8) ? 2 : 1) gemv_kernel(con
                     va += src[(2 * rp) * NT + t];
                     vb += src[(2 * rp + 1) * NT + t];
                 }
-                gemv_epilogue<T>(a, p, t, va, vb);
+                gemv_epilogue<T>(a, p, t, va, vb, pre);
             }
         }
     }

@@ -57,8 +57,22 @@ __device__ __forceinline__ float swiglu_act(float gate, float up) {
     return gate * __fdividef(1.f, 1.f + expf(-gate)) * up;
 }
 
+// Values an epilogue would otherwise fetch from global memory behind the weight stream: the per-token constants of the
+// RoPE / KV-append epilogue (position, cache page, sin and cos rows; head sizes up to 128), staged in shared memory
+// before the main loop, and the residual pair of this output, loaded before the group's arithmetic.
+struct RopeStage {
+    uint32_t pos[4];
+    int page[4];
+    float sn[4][64], cs[4][64];
+};
+struct EpiPre {
+    const RopeStage *rope = nullptr;  // EPI_ROPE_KV
+    uint32_t res = 0;                 // EPI_RESIDUAL: the packed residual pair
+    bool has_res = false;
+};
+
 template <class T>
-__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb) {
+__device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, float vb, const EpiPre &pre = EpiPre()) {
     T *y = reinterpret_cast<T *>(a.y);
     switch (a.epilogue) {
     case EPI_STORE: {
@@ -81,7 +95,7 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         size_t r = (size_t)pair * 2;
         const T *res = reinterpret_cast<const T *>(a.res) + (size_t)t * a.stride_res + r;
         // residual enters as the beta = 1 operand of the GEMM: one rounding of acc + res
-        uint32_t rr = *reinterpret_cast<const uint32_t *>(res);
+        uint32_t rr = pre.has_res ? pre.res : *reinterpret_cast<const uint32_t *>(res);
         float2 rf = Act<T>::to_f2(rr);
         const uint32_t packed = Act<T>::pack(va + rf.x, vb + rf.y);
         if (a.push.n) {
@@ -103,10 +117,11 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         int sect = r < a.qd ? 0 : (r < a.qd + a.kvd ? 1 : 2);
         int rr = r - (sect == 0 ? 0 : (sect == 1 ? a.qd : a.qd + a.kvd));
         int head = rr / a.dh, e = rr - head * a.dh;
-        uint32_t p = a.pos[t];
+        uint32_t p = pre.rope ? pre.rope->pos[t] : a.pos[t];
         if (sect < 2) {
             int half_dh = a.dh >> 1;
-            float sn = a.sin_t[(size_t)p * half_dh + (e >> 1)], cs = a.cos_t[(size_t)p * half_dh + (e >> 1)];
+            float sn = pre.rope ? pre.rope->sn[t][e >> 1] : a.sin_t[(size_t)p * half_dh + (e >> 1)];
+            float cs = pre.rope ? pre.rope->cs[t][e >> 1] : a.cos_t[(size_t)p * half_dh + (e >> 1)];
             float ya = xa * cs - xb * sn, yb = xa * sn + xb * cs;
             xa = ya;
             xb = yb;
@@ -115,8 +130,7 @@ __device__ void gemv_epilogue(const GemvArgs &a, int pair, int t, float va, floa
         if (sect == 0) {
             *reinterpret_cast<uint32_t *>(&y[(size_t)t * a.stride_y + r]) = packed;
         } else {
-            int seq = a.tok_seq[t];
-            int page = a.page_table[(size_t)seq * a.pt_stride + (p >> a.geom.page_shift)];
+            int page = pre.rope ? pre.rope->page[t] : a.page_table[(size_t)a.tok_seq[t] * a.pt_stride + (p >> a.geom.page_shift)];
             int slot = p & (a.geom.page_tokens - 1);
             size_t off = a.geom.block_off(page, a.layer, sect - 1, head) + (size_t)slot * a.dh + e;
             *reinterpret_cast<uint32_t *>(reinterpret_cast<T *>(a.kv_pool) + off) = packed;
