@@ -308,7 +308,8 @@ def tp_parity(L, env):
             "ok": bool(ids_equal == total and worst <= 2e-2 and not any(status))}
 
 
-def run_decode(L, env, cfg, batch, prompt_range, steps, warmup, want_e2e=True, want_roofline=True, max_prefill=1024):
+def run_decode(L, env, cfg, batch, prompt_range, steps, warmup, want_e2e=True, want_roofline=True, max_prefill=1024,
+               timeline=None):
     """Loads the model (this rank's slice), prefills, then times `steps` decode rounds with CUDA events.
     Returns a dict of results; the caller prints."""
     import numpy as np
@@ -378,6 +379,29 @@ def run_decode(L, env, cfg, batch, prompt_range, steps, warmup, want_e2e=True, w
         ms = env.max_over_ranks(ev0.elapsed_time(ev1))
         res.update(ms_per_step=ms / steps, value=batch * steps / (ms / 1e3), clocks=clocks.summary(),
                    launches_per_step=ctx.last_launch_count, step_bytes=step_bytes / steps)
+
+        # ---- device timeline of one decode step (outside the timed region): start and end of every kernel as CUPTI
+        # reports them through torch.profiler, overlaps of programmatically launched kernels included
+        if timeline and rank == 0:
+            from torch.profiler import ProfilerActivity, profile
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(4):
+                    decode_round(zeros, fast_map)
+                stream.synchronize()
+            ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                        key=lambda e: e.time_range.start)
+            marks = [i for i, e in enumerate(ev) if "fast_embedding" in e.name]
+            if len(marks) >= 2:
+                t0 = ev[marks[-2]].time_range.start
+                with open(timeline, "w") as f:
+                    f.write("# kernel | start us | end us | duration us   (one decode step, batch %d, %d layers)\n" % (batch, cfg.n_layers))
+                    for e in ev[marks[-2]:marks[-1]]:
+                        f.write("%-72s %9.2f %9.2f %8.2f\n" % (e.name[:72], e.time_range.start - t0, e.time_range.end - t0,
+                                                              e.time_range.end - e.time_range.start))
+                    f.write("# step: %.2f us\n" % (ev[marks[-1]].time_range.start - t0))
+        elif timeline:
+            for _ in range(4):
+                decode_round(zeros, fast_map)
 
         # ---- end to end: host tokens in (pinned staging inside lcu_step), sampled pair read back every step
         if want_e2e:
@@ -472,6 +496,8 @@ def main():
     ap.add_argument("--no-head-sharding", action="store_true", help="N > 1: LM head on the lead rank alone, as in the reference")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                     help="library tuning value (lcu_set_tuning), e.g. pdl_edges=29; for A/B measurements")
+    ap.add_argument("--timeline", default=None, metavar="PATH",
+                    help="after the timed region: write start / end of every kernel of one decode step (CUPTI via torch.profiler)")
     ap.add_argument("--layers", type=int, default=0, metavar="N",
                     help="cut the model to its first N layers: a small case for profiler captures, not a bench line")
     ap.add_argument("--probe-linear", type=int, default=0, metavar="TOKENS",
@@ -545,7 +571,7 @@ def main():
         parity = tp_parity(L, env)
 
     # ---- the headline workload
-    res = run_decode(L, env, cfg, batch, prange, args.steps, args.warmup, want_e2e=not args.no_e2e)
+    res = run_decode(L, env, cfg, batch, prange, args.steps, args.warmup, want_e2e=not args.no_e2e, timeline=args.timeline)
     config["tp_collectives"] = res["tp_collectives"]
     bad_status = any(res["device_status_all_ranks"])
 
