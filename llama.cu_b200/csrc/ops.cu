@@ -12,6 +12,9 @@ namespace lcu {
 template <class U>
 __global__ void embedding_kernel(U *__restrict__ out, const U *__restrict__ table,
                                  const uint32_t *__restrict__ index, int units) {
+    // a programmatic dependent (the first projection of the step) may start now: it streams its first weights while
+    // this copy runs and waits for it before touching the activations
+    grid_dep_launch();
     grid_dep_wait();
     size_t row = index[blockIdx.x];
     const U *src = table + row * units;
@@ -39,6 +42,7 @@ int op_embedding(void *out, const void *table, const uint32_t *index, int n, siz
 // op/fast_embedding.cuh:7-15: tokens[map[i].v] = kv_pairs[map[i].k].k
 __global__ void fast_embedding_kernel(uint32_t *__restrict__ tokens, const lcu_kv_pair *__restrict__ pairs,
                                       const uint2 *__restrict__ map, int n) {
+    grid_dep_launch();
     grid_dep_wait();
     int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
