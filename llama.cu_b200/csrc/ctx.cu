@@ -596,8 +596,6 @@ int lcu_set_tuning(lcu_ctx *c, const char *key, long long value) {
     else if (k == "gemv_ctas_per_sm") { LCU_REQUIRE(value >= 1 && value <= 2, "set_tuning: gemv_ctas_per_sm = %lld (1, 2)", value); t.gemv_ctas_per_sm = (int)value; }
     else if (k == "q8_rows") { LCU_REQUIRE(value == 1 || value == 2 || value == 4, "set_tuning: q8_rows = %lld (1, 2, 4)", value); t.q8_rows = (int)value; }
     else if (k == "gemv_lean_norm") t.gemv_lean_norm = value != 0;
-    else if (k == "pdl_o_trigger") t.pdl_o_trigger = (int)value;
-    else if (k == "attn_trigger") t.attn_trigger = (int)value;
     else if (k == "tc") t.tc = value != 0;
     else if (k == "tc_block") { LCU_REQUIRE(value == 64 || value == 128 || value == 256, "set_tuning: tc_block = %lld (64, 128, 256)", value); t.tc_block = (int)value; }
     else if (k == "tc_cluster") { LCU_REQUIRE(value >= 0 && value <= 2, "set_tuning: tc_cluster = %lld (0..2)", value); t.tc_cluster = (int)value; }
@@ -735,8 +733,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
     auto linear = [&](GemvArgs proto, int n, const void *xin, int stride_in, void *yout, int stride_out, bool norm,
                       const void *norm_w, bool push = false, int edge_in = -1, int edge_out = -1) -> int {
         const bool pdl_in = pdl || (edge_in >= 0 && ((pdl_edges >> edge_in) & 1));
-        int trig = (edge_out >= 0 && ((pdl_edges >> edge_out) & 1)) ? 0 : pdl_trigger;
-        if (edge_in == 1 && pdl_in && tuning().pdl_o_trigger >= 0) trig = tuning().pdl_o_trigger;
+        const int trig = (edge_out >= 0 && ((pdl_edges >> edge_out) & 1)) ? 0 : pdl_trigger;
         linear_ctas = 0;
         const void *src = xin;
         int src_stride = stride_in;
@@ -823,7 +820,7 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
             // rows of earlier rounds before it waits; its own dependents start once its first tile has landed
             const bool attn_pdl = pdl || (!batched && (pdl_edges & 1));
             a.early_kv = (attn_pdl && r.decode_only) ? 1 : 0;
-            a.pdl_trigger = tuning().attn_trigger;
+            a.pdl_trigger = 1;
             // rounds that hold prompts: 64 query rows per CTA share every K/V tile (prefill form)
             if (r.n_groups > 0) rc = attn_prefill_launch(a, D + r.L.groups, r.n_groups, dt, s);
             else rc = attn_launch(a, dt, s, attn_pdl);
