@@ -66,12 +66,24 @@ template <class T, class Tw>
 __global__ void rms_norm_kernel(T *__restrict__ y, int sy, const T *__restrict__ x, int sx,
                                 const Tw *__restrict__ w, float eps, int d) {
     grid_dep_launch();  // a GEMM launched with the programmatic attribute may start streaming its weights now
-    grid_dep_wait();
     const T *xr = x + (size_t)blockIdx.x * sx;
     T *yr = y + (size_t)blockIdx.x * sy;
     // 128-bit path when the row and both strides allow it; the row stays in registers between passes
     const bool vec = (d % 8 == 0) && (sx % 8 == 0) && (sy % 8 == 0) && d <= 8 * 4 * (int)blockDim.x &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w)) % 16 == 0);
+    // 16-bit norm weights are constants: they are requested before the dependency wait (and, in any case, together with
+    // the row instead of after the reduction: one round trip to L2 less on the critical path)
+    uint4 wk[4];
+    if constexpr (sizeof(Tw) == 2) {
+        if (vec) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int i = threadIdx.x + j * blockDim.x;
+                wk[j] = i < d / 8 ? __ldg(reinterpret_cast<const uint4 *>(w) + i) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    }
+    grid_dep_wait();
     uint4 keep[4];
     float acc = 0.f;
     if (vec) {
@@ -117,7 +129,7 @@ __global__ void rms_norm_kernel(T *__restrict__ y, int sy, const T *__restrict__
                     float4 w0 = reinterpret_cast<const float4 *>(w)[2 * i], w1 = reinterpret_cast<const float4 *>(w)[2 * i + 1];
                     wf[0] = w0.x; wf[1] = w0.y; wf[2] = w0.z; wf[3] = w0.w; wf[4] = w1.x; wf[5] = w1.y; wf[6] = w1.z; wf[7] = w1.w;
                 } else {
-                    uint4 wv = reinterpret_cast<const uint4 *>(w)[i];
+                    const uint4 wv = wk[j];
                     float2 a = Act<T>::to_f2(wv.x), b = Act<T>::to_f2(wv.y), c = Act<T>::to_f2(wv.z), e = Act<T>::to_f2(wv.w);
                     wf[0] = a.x; wf[1] = a.y; wf[2] = b.x; wf[3] = b.y; wf[4] = c.x; wf[5] = c.y; wf[6] = e.x; wf[7] = e.y;
                 }
