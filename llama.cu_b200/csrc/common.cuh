@@ -36,6 +36,7 @@ inline cudaStream_t as_stream(lcu_stream_t s) { return reinterpret_cast<cudaStre
 struct Tuning {
     int pdl_edges = -1;            // bit per layer edge launched as a programmatic dependent; -1: 28 (GEMV rounds) / 30 (batched)
     int gemv_lean_norm = 1;        // GEMV: one-token RMSNorm prologue from registers
+    int rms_pdl = 1;               // batched rounds on the tcgen05 kernels: the stand-alone RMSNorm is a programmatic dependent
     int gemv_ctas_per_sm = 2;      // GEMV CTAs per SM (read at a shape's first launch)
     int q8_rows = 4;               // Q8_0 GEMV: row pairs per thread
     int tc = 1;                    // 0: keep the tcgen05 kernel out (mma.sync kernel for every batched round)

@@ -596,6 +596,7 @@ int lcu_set_tuning(lcu_ctx *c, const char *key, long long value) {
     else if (k == "gemv_ctas_per_sm") { LCU_REQUIRE(value >= 1 && value <= 2, "set_tuning: gemv_ctas_per_sm = %lld (1, 2)", value); t.gemv_ctas_per_sm = (int)value; }
     else if (k == "q8_rows") { LCU_REQUIRE(value == 1 || value == 2 || value == 4, "set_tuning: q8_rows = %lld (1, 2, 4)", value); t.q8_rows = (int)value; }
     else if (k == "gemv_lean_norm") t.gemv_lean_norm = value != 0;
+    else if (k == "rms_pdl") t.rms_pdl = value != 0;
     else if (k == "tc") t.tc = value != 0;
     else if (k == "tc_block") { LCU_REQUIRE(value == 64 || value == 128 || value == 256, "set_tuning: tc_block = %lld (64, 128, 256)", value); t.tc_block = (int)value; }
     else if (k == "tc_cluster") { LCU_REQUIRE(value >= 0 && value <= 2, "set_tuning: tc_cluster = %lld (0..2)", value); t.tc_cluster = (int)value; }
@@ -738,7 +739,10 @@ int enqueue_round(lcu_ctx *c, const Round &r, lcu_kv_pair *out_dev, cudaStream_t
         const void *src = xin;
         int src_stride = stride_in;
         if (batched && norm) {
-            int rc2 = op_rms_norm(c->hbuf, d.d, xin, stride_in, norm_w, norm_dt, d.eps, n, d.d, dt, s, pdl);
+            // launched as a programmatic dependent where the tcgen05 kernels follow (8B batch 32: 4.94 -> 4.85 ms, 70B per-rank
+            // step: 8.35 -> 8.23 ms); ahead of the mma.sync kernels of Q8_0 rounds it costs (batch 16: 4.90 -> 5.34 ms)
+            const bool rms_pdl = tuning().rms_pdl && tc_on && n > 8 && gemm_tc_supported(proto.in, proto.w_q8);
+            int rc2 = op_rms_norm(c->hbuf, d.d, xin, stride_in, norm_w, norm_dt, d.eps, n, d.d, dt, s, pdl || rms_pdl);
             if (rc2) return rc2;
             ++launches;
             src = c->hbuf;
