@@ -182,7 +182,9 @@ LCU_API int lcu_set_wait_limit_us(lcu_ctx *ctx, long long us);
 /* Process-wide tuning values; the defaults are what the committed measurements use.  Keys: "pdl_edges" (bit per
  * layer edge launched as a programmatic dependent: 0 QKV->attention, 1 attention->O, 2 O->gate|up, 3 gate|up->down,
  * 4 down->next QKV, 5 last down->LM head; -1 = default), "gemv_ctas_per_sm" (1, 2; read at a shape's first launch),
- * "q8_rows" (1, 2, 4), "tc" (0: no tcgen05 kernel), "tc_cluster" (0..2), "p2p_scatter_ranks", "p2p_scatter_min".
+ * "q8_rows" (1, 2, 4), "tc" (0: no tcgen05 kernel), "tc_block" (64, 128, 256), "tc_cluster" (0..2),
+ * "p2p_scatter_ranks", "p2p_scatter_min", "gemv_lean_norm" (0: general RMSNorm prologue in the one-token GEMV),
+ * "rms_pdl" (0: the stand-alone RMSNorm of batched rounds is a plain launch).
  * `ctx` (may be NULL) drops its captured rounds.  A measurement aid without counterpart in the reference. */
 LCU_API int lcu_set_tuning(lcu_ctx *ctx, const char *key, long long value);
 /* Tensor parallelism over peer memory: 1 (default) = arg-max rounds shard the LM head by vocabulary rows — every rank
