@@ -19,7 +19,12 @@
 //   - the first group's loads are issued BEFORE griddepcontrol.wait, so under programmatic
 //     dependent launch the weights of this GEMV already stream while the previous kernel
 //     of the step drains; only then are the activations staged to shared memory;
-//   - Q8_0 weights (int8 quants + one f16 scale per 32) are dequantised in registers.
+//   - Q8_0 weights (int8 quants + one f16 scale per 32) are dequantised in registers;
+//   - nothing an epilogue needs is fetched behind the weight stream: the per-token constants of the
+//     RoPE / KV-append epilogue sit in shared memory before the dependency wait, the residual pair of
+//     a row pair is requested at the start of its group;
+//   - the prologue is a template parameter, so the plain kernels carry no RMSNorm code; the one-token
+//     RMSNorm form works from registers with the norm weights fetched before the wait.
 #include <type_traits>
 
 #include "gemv.cuh"
