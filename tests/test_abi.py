@@ -94,6 +94,21 @@ def test_invalid_descriptions_are_rejected(L):
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_tuning_keys_are_validated(L):
+    """lcu_set_tuning accepts the documented keys (restoring their defaults here) and refuses anything else; it needs
+    neither a context nor a GPU."""
+    defaults = {"pdl_edges": -1, "gemv_ctas_per_sm": 2, "q8_rows": 4, "gemv_lean_norm": 1, "rms_pdl": 1, "tc": 1,
+                "tc_block": 256, "tc_cluster": 1, "p2p_scatter_ranks": 8, "p2p_scatter_min": 131072}
+    for key, value in defaults.items():
+        L.set_tuning(key, value)
+    with pytest.raises(L.LcuError):
+        L.set_tuning("no_such_key", 1)
+    with pytest.raises(L.LcuError):
+        L.set_tuning("tc_block", 96)
+    with pytest.raises(L.LcuError):
+        L.set_tuning("gemv_ctas_per_sm", 3)
+
+
 def test_no_cpu_fallback(L):
     """Without a device the product path fails loudly instead of computing on the host."""
     with pytest.raises(L.LcuError) as e:
