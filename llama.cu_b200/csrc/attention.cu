@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnArgs a) {
     if (a.tiles_per_split > tps) tps = a.tiles_per_split;
     const int my_splits = (n_tiles + tps - 1) / tps;
     // cluster_z > 0: the splits of a (token, KV head) are one thread-block cluster and merge through distributed
-    // shared memory; CTAs without work still take part in its two barriers
+    // shared memory; CTAs without work still take part in its barrier
     const bool clus = a.cluster_z > 0;
     if (sp >= my_splits) {
         if (clus) att_cluster_sync();

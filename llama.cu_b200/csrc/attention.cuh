@@ -26,8 +26,8 @@ struct AttnArgs {
     int n_splits;          // grid depth = most splits any token of the round can need
     int tiles_per_split;   // 64-position tiles one CTA walks (0: context / n_splits); a token with a short
                            // context uses fewer splits and the CTAs beyond them exit at once
-    int cluster_z;         // > 0 (== n_splits, <= 8): the splits form a thread-block cluster and merge through
-                           // distributed shared memory instead of the scratch below
+    int cluster_z;         // > 0 (== n_splits, <= 8): the splits form a thread-block cluster; each stores its partial into
+                           // the first split's shared memory, which merges after one cluster barrier (no scratch)
     // Programmatic dependent launch.  early_kv: the round holds ONE new token per sequence, so every cached row below
     // a token's own position was written by an earlier round and may be fetched before the wait on the predecessor
     // (which writes only the new row).  pdl_trigger: 0 = dependents may start as soon as this grid is resident,
